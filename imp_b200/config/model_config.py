@@ -15,6 +15,15 @@ from typing import Any, Dict, Optional
 from ..capi import ConfigError  # noqa: F401  (re-exported)
 
 
+def architecture_name(d: Dict[str, Any]) -> Optional[str]:
+    """The model class a config.json names: `architectures[0]`, or the single string `architecture`."""
+    archs = d.get("architectures") if isinstance(d, dict) else None
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = d.get("architecture") if isinstance(d, dict) and archs is None else None
+    return one if isinstance(one, str) else None
+
+
 class ModelConfig:
     """The keys every decoder has; everything else stays reachable through `.extra` and `.raw`."""
 
@@ -34,7 +43,7 @@ class ModelConfig:
     # ---- fields ----------------------------------------------------------
     @property
     def architecture(self) -> str:
-        return self.raw["architectures"][0]
+        return architecture_name(self.raw)
 
     @property
     def eos_token_ids(self):
@@ -108,3 +117,24 @@ class Qwen3Config(ModelConfig):
             return 0
         first = self.raw.get("max_window_layers")
         return sw if layer >= (first if first is not None else 0) else 0
+
+
+class KazedraConfig(ModelConfig):
+    """Kazedra (`"architecture": "Kazedra"`): `vocab`, `width`, `norm.eps`, `logit_scale` and a list `layers`, each
+    entry with `type` ("parallel"), the sizes and constants of its two mixers under `mixer.left` / `mixer.right`, the
+    weights `mixer.left_scale` / `mixer.right_scale`, and `mlp` (`{"kind": "dense", "ff": n}` or null)."""
+
+    KNOWN_KEYS = ("architecture", "vocab", "width", "norm", "logit_scale", "layers", "torch_dtype", "dtype", "eos_token_id",
+                  "bos_token_id", "max_positions", "bias_buckets")
+
+    @property
+    def vocab_size(self) -> int:
+        return int(self.raw["vocab"])
+
+    @property
+    def hidden_size(self) -> int:
+        return int(self.raw["width"])
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.raw["layers"])

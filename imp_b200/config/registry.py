@@ -17,11 +17,11 @@ import os
 from typing import Any, Callable, Dict, Type
 
 from .. import capi
-from .model_config import ConfigError, ModelConfig, Qwen3Config
+from .model_config import ConfigError, KazedraConfig, ModelConfig, Qwen3Config, architecture_name
 
 # architectures registered from Python: name -> (config class, plan function, C callback kept alive)
 _PY_ARCHS: Dict[str, tuple] = {}
-_BUILTIN_CONFIGS: Dict[str, Type[ModelConfig]] = {"Qwen3ForCausalLM": Qwen3Config}
+_BUILTIN_CONFIGS: Dict[str, Type[ModelConfig]] = {"Qwen3ForCausalLM": Qwen3Config, "Kazedra": KazedraConfig}
 
 
 def parse_config_dict(d: Dict[str, Any], where: str = "config.json") -> Dict[str, Any]:
@@ -74,13 +74,13 @@ def config_class_of(name: str) -> Type[ModelConfig]:
 
 
 def config_from_dict(d: Dict[str, Any], where: str = "config.json") -> ModelConfig:
-    archs = d.get("architectures") if isinstance(d, dict) else None
-    if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
+    name = architecture_name(d)
+    if name is None:
         raise ConfigError(capi.IMP_ERROR_INVALID_MODEL, f"{where}: 'architectures' must be a list that names the model class")
-    if archs[0] not in known_architectures():
+    if name not in known_architectures():
         raise ConfigError(capi.IMP_ERROR_INVALID_MODEL,
-                          f"unknown architecture '{archs[0]}'; known: {', '.join(known_architectures()) or '(none)'}")
-    return config_class_of(archs[0]).from_json_dict(d, where)
+                          f"unknown architecture '{name}'; known: {', '.join(known_architectures()) or '(none)'}")
+    return config_class_of(name).from_json_dict(d, where)
 
 
 def load_config(model_dir: str) -> ModelConfig:

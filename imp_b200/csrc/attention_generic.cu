@@ -16,6 +16,11 @@
 // kernels, which see only the call's own K and V (src/graph/executor_forward.cu:
 // 568-604), keys come from the pages, so a later portion of a prompt sees the
 // earlier ones.
+//
+// Two optional additions for mixers that are not plain softmax attention (both in 32-bit, after
+// the scale): `bias` adds bias[h][min(p - j, n_dist - 1)] to the score of key j, a table by
+// distance and query head; `sink` adds exp(sink[h]) to the softmax denominator, a term without a
+// key or a value.
 #include "common.cuh"
 
 constexpr int ATT_BLOCK = 128;
@@ -27,7 +32,7 @@ __global__ void paged_attention_generic_kernel(
     const TA* __restrict__ k_cache, const TA* __restrict__ v_cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
     const int* __restrict__ positions, int n_seqs, int Hq, int Hkv, int Dh, int page_size, int num_pages,
-    float scale, int window, int* status) {
+    float scale, int window, const float* __restrict__ bias, int n_dist, const float* __restrict__ sink, int* status) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float q_s[ATT_MAX_DH];
@@ -51,6 +56,7 @@ __global__ void paged_attention_generic_kernel(
 
     const int* bt = block_table + (int64_t)seq * bt_stride;
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const float* bias_h = bias ? bias + (int64_t)h * n_dist : nullptr;
     float m = -INFINITY, l = 0.f;
     float acc0 = 0.f, acc1 = 0.f;  // dims tid and tid + ATT_BLOCK
 
@@ -68,6 +74,7 @@ __global__ void paged_attention_generic_kernel(
                 float dot = 0.f;
                 for (int d = 0; d < Dh; ++d) dot = fmaf(q_s[d], to_float(kp[d]), dot);
                 s = dot * scale;
+                if (bias_h) s += bias_h[min(pos - j, n_dist - 1)];
             }
         }
         const float m_new = fmaxf(m, block_max(s, scratch));
@@ -93,6 +100,15 @@ __global__ void paged_attention_generic_kernel(
         }
         __syncthreads();  // p_s/off_s are rewritten by the next chunk
     }
+    if (sink) {
+        // one more term of the denominator: exp(sink) against the running maximum
+        const float sk = sink[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+        acc0 *= corr;
+        acc1 *= corr;
+    }
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
     if (tid < Dh) o[tid] = from_float<TA>(acc0 * inv_l);
     if (tid + ATT_BLOCK < Dh) o[tid + ATT_BLOCK] = from_float<TA>(acc1 * inv_l);
@@ -100,11 +116,11 @@ __global__ void paged_attention_generic_kernel(
 
 // out: [n_tokens, out_stride] (head h at column h*Dh); q likewise with q_stride.
 // k_cache, v_cache: [num_pages, Hkv, page_size, Dh] of one layer.
-IMP_API int imp_paged_attention_generic(
+static int launch_generic(
     void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
     const int* block_table, int bt_stride, const int* seq_of_token, const int* positions, int n_tokens,
-    int n_seqs, int Hq, int Hkv, int Dh, int page_size, int num_pages, float scale, int window, int dtype,
-    int* status, void* stream) {
+    int n_seqs, int Hq, int Hkv, int Dh, int page_size, int num_pages, float scale, int window, const float* bias,
+    int n_dist, const float* sink, int dtype, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(out && q && k_cache && v_cache && block_table && seq_of_token && positions,
                   "imp_paged_attention_generic: null pointer");
@@ -118,11 +134,34 @@ IMP_API int imp_paged_attention_generic(
         paged_attention_generic_kernel<float><<<grid, ATT_BLOCK, 0, s>>>(
             (float*)out, out_stride, (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache,
             block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, Dh, page_size, num_pages, scale,
-            window, status);
+            window, bias, n_dist, sink, status);
     else
         paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_BLOCK, 0, s>>>(
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
             (const __nv_bfloat16*)v_cache, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, Dh,
-            page_size, num_pages, scale, window, status);
+            page_size, num_pages, scale, window, bias, n_dist, sink, status);
     IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_paged_attention_generic(
+    void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+    const int* block_table, int bt_stride, const int* seq_of_token, const int* positions, int n_tokens,
+    int n_seqs, int Hq, int Hkv, int Dh, int page_size, int num_pages, float scale, int window, int dtype,
+    int* status, void* stream) {
+    return launch_generic(out, out_stride, q, q_stride, k_cache, v_cache, block_table, bt_stride, seq_of_token, positions,
+                          n_tokens, n_seqs, Hq, Hkv, Dh, page_size, num_pages, scale, window, nullptr, 0, nullptr, dtype,
+                          status, stream);
+}
+
+// The same with a score bias by distance, bias [Hq, n_dist] (float32; null = none), and a sink per
+// query head, sink [Hq] (float32; null = none).
+IMP_API int imp_paged_attention_generic_bias(
+    void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+    const int* block_table, int bt_stride, const int* seq_of_token, const int* positions, int n_tokens,
+    int n_seqs, int Hq, int Hkv, int Dh, int page_size, int num_pages, float scale, int window, const float* bias,
+    int n_dist, const float* sink, int dtype, int* status, void* stream) {
+    IMP_CHECK_ARG(!bias || n_dist > 0, "imp_paged_attention_generic_bias: a bias table needs at least one distance");
+    return launch_generic(out, out_stride, q, q_stride, k_cache, v_cache, block_table, bt_stride, seq_of_token, positions,
+                          n_tokens, n_seqs, Hq, Hkv, Dh, page_size, num_pages, scale, window, bias, n_dist, sink, dtype,
+                          status, stream);
 }

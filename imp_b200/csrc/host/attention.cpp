@@ -284,11 +284,20 @@ static bool prefill_tc_supported(const Tensor& q, const Tensor& out, const Atten
 }
 
 void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
-                     const std::vector<int>& tiling_ids) {
+                     const std::vector<int>& tiling_ids, const AttentionExtras* extras) {
     Runtime& rt = *st.rt;
     check_cache(cache, g);
     const ImpCacheView& c = cache.view;
     need(rows(out) == rows(q) && out.dtype == q.dtype, "attention: out and q must agree");
+    if (extras && (extras->bias || extras->sink)) {
+        ++rt.launches;
+        check_launch(imp_paged_attention_generic_bias(out.data, out.stride0, q.data, q.stride0, c.k_pages, c.v_pages, c.block_table,
+                                                      c.bt_stride, st.view.seq_of_token, st.view.positions, (int)rows(q), st.B(),
+                                                      g.hq, g.hkv, g.dh, c.page_size, c.num_pages, g.scale, g.window, extras->bias,
+                                                      extras->n_dist, extras->sink, q.dtype, rt.status, rt.stream),
+                     "paged_attention_generic_bias");
+        return;
+    }
     if (rt.is_f32()) {
         ++rt.launches;
         check_launch(imp_paged_attention_generic(out.data, out.stride0, q.data, q.stride0, c.k_pages, c.v_pages, c.block_table,

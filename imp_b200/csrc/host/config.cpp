@@ -232,6 +232,176 @@ ModelPlan qwen3_plan(const Qwen3Config& cfg) {
     return plan;
 }
 
+// ------------------------------------------------------------------------------------ Kazedra
+namespace {
+const Json& require_object(const Json& d, const std::string& key, const std::string& where) {
+    const Json& v = require(d, key, where);
+    if (!v.is_object()) bad(where + ": key '" + key + "' must be an object, got " + v.type_name());
+    return v;
+}
+}  // namespace
+
+KazedraConfig KazedraConfig::from_json(const Json& d, const std::string& where) {
+    KazedraConfig c;
+    c.architecture = d.get_string("architecture", "Kazedra");
+    c.vocab_size = positive("vocab", require_int(d, "vocab", where), where);
+    c.hidden_size = positive("width", require_int(d, "width", where), where);
+    c.max_position_embeddings = positive("max_positions", d.get_int("max_positions", 1 << 20), where);
+    c.torch_dtype = d.get_string("torch_dtype", d.get_string("dtype", "bfloat16"));
+    if (c.torch_dtype != "bfloat16" && c.torch_dtype != "float32")
+        bad(where + ": torch_dtype '" + c.torch_dtype + "' is not supported (bfloat16 or float32)");
+    if (const Json* eos = d.find("eos_token_id")) {
+        if (eos->is_array()) {
+            for (const auto& e : eos->items())
+                if (e.is_int()) c.eos_token_ids.push_back((int)e.as_int());
+        } else if (eos->is_int()) {
+            c.eos_token_ids.push_back((int)eos->as_int());
+        }
+    }
+    c.bos_token_id = d.get_int("bos_token_id", -1);
+    c.raw = d;
+    c.norm_eps = require_float(require_object(d, "norm", where), "eps", where + ": norm");
+    if (!(c.norm_eps > 0)) bad(where + ": norm.eps must be positive");
+    c.logit_scale = d.get_double("logit_scale", 1.0);
+    const Json& layers = require(d, "layers", where);
+    if (!layers.is_array() || layers.size() == 0) bad(where + ": 'layers' must be a non-empty list");
+    int i = 0;
+    for (const Json& lj : layers.items()) {
+        const std::string lw = where + ": layers[" + std::to_string(i++) + "]";
+        if (!lj.is_object()) bad(lw + " must be an object");
+        Layer l;
+        l.type = lj.get_string("type", "");
+        if (l.type != "parallel") bad(lw + ": unknown layer type '" + l.type + "' (known: parallel)");
+        const Json& m = require_object(lj, "mixer", lw);
+        const Json& a = require_object(m, "left", lw + ".mixer");
+        const std::string aw = lw + ".mixer.left", bw = lw + ".mixer.right";
+        l.left.heads = positive("heads", require_int(a, "heads", aw), aw);
+        l.left.kv_heads = positive("kv_heads", require_int(a, "kv_heads", aw), aw);
+        l.left.dim = positive("dim", require_int(a, "dim", aw), aw);
+        l.left.vdim = positive("vdim", a.get_int("vdim", l.left.dim), aw);
+        l.left.bias_max = positive("bias_max", require_int(a, "bias_max", aw), aw);
+        l.left.scale = require_float(a, "scale", aw);
+        if (const Json* qt = a.find("q_temp")) {
+            if (qt->is_object()) {
+                l.left.temp_coef = require_float(*qt, "coef", aw + ".q_temp");
+                l.left.temp_every = positive("every", require_int(*qt, "every", aw + ".q_temp"), aw + ".q_temp");
+            }
+        }
+        if (l.left.heads % l.left.kv_heads) bad(aw + ": heads " + std::to_string(l.left.heads) + " must be a multiple of kv_heads " + std::to_string(l.left.kv_heads));
+        if (l.left.vdim != l.left.dim) bad(aw + ": the values are the keys, so vdim " + std::to_string(l.left.vdim) + " must equal dim " + std::to_string(l.left.dim));
+        const Json& b = require_object(m, "right", lw + ".mixer");
+        l.right.heads = positive("heads", require_int(b, "heads", bw), bw);
+        l.right.kv_heads = positive("kv_heads", require_int(b, "kv_heads", bw), bw);
+        l.right.dim = positive("dim", require_int(b, "dim", bw), bw);
+        l.right.vdim = positive("vdim", require_int(b, "vdim", bw), bw);
+        l.right.conv = positive("conv", require_int(b, "conv", bw), bw);
+        if (l.right.heads % l.right.kv_heads) bad(bw + ": heads " + std::to_string(l.right.heads) + " must be a multiple of kv_heads " + std::to_string(l.right.kv_heads));
+        l.left_scale = require_float(m, "left_scale", lw + ".mixer");
+        l.right_scale = require_float(m, "right_scale", lw + ".mixer");
+        if (const Json* f = lj.find("mlp")) {
+            if (f->is_object()) {
+                const std::string kind = f->get_string("kind", "");
+                if (kind != "dense") bad(lw + ".mlp: unknown kind '" + kind + "' (known: dense)");
+                l.ff = positive("ff", require_int(*f, "ff", lw + ".mlp"), lw + ".mlp");
+            } else if (!f->is_null()) {
+                bad(lw + ".mlp must be an object or null");
+            }
+        }
+        c.layers.push_back(l);
+    }
+    c.num_hidden_layers = (int64_t)c.layers.size();
+    return c;
+}
+
+Json KazedraConfig::to_json() const {
+    Json j = raw.is_object() ? raw : Json::object();
+    j["architecture"] = architecture;
+    j["vocab"] = vocab_size;
+    j["width"] = hidden_size;
+    j["torch_dtype"] = torch_dtype;
+    j.erase("dtype");
+    return j;
+}
+
+// Layer i's tensors are 'l<i>.norm1', 'l<i>.mix.left.*', 'l<i>.mix.right.*', 'l<i>.norm2', 'l<i>.mlp.*'; the
+// norm weights are stored around zero (weight_offset 1).  A model-wide `bias_buckets` key, when present, fixes
+// the rows of the distance-bias tables (random weights need it); otherwise the checkpoint's tables decide.
+ModelPlan kazedra_plan(const KazedraConfig& cfg) {
+    const int64_t d = cfg.hidden_size;
+    ModelPlan plan;
+    plan.architecture = cfg.architecture;
+    plan.hidden_size = d;
+    plan.vocab_size = cfg.vocab_size;
+    plan.max_positions = cfg.max_position_embeddings;
+    auto norm = [&](const std::string& tensor) {
+        PartSpec n;
+        n.kind = "rmsnorm";
+        n.params["size"] = d;
+        n.params["eps"] = cfg.norm_eps;
+        n.params["weight_offset"] = 1.0;
+        n.tensors = {{"weight", tensor}};
+        return n;
+    };
+    const int64_t buckets = cfg.raw.is_object() ? cfg.raw.get_int("bias_buckets", 0) : 0;
+    for (size_t i = 0; i < cfg.layers.size(); ++i) {
+        const KazedraConfig::Layer& l = cfg.layers[i];
+        const std::string p = "l" + std::to_string(i) + ".", a = p + "mix.left.", b = p + "mix.right.";
+        PartSpec left;
+        left.kind = "sink_bias_attention";
+        left.params["hidden_size"] = d;
+        left.params["num_heads"] = l.left.heads;
+        left.params["num_kv_heads"] = l.left.kv_heads;
+        left.params["head_dim"] = l.left.dim;
+        left.params["scale"] = l.left.scale;
+        left.params["norm_eps"] = cfg.norm_eps;
+        left.params["q_temp_coef"] = l.left.temp_coef;
+        left.params["q_temp_every"] = l.left.temp_every;
+        left.params["bias_max_distance"] = l.left.bias_max;
+        left.params["bias_buckets"] = buckets;
+        left.tensors = {{"q_proj", a + "q"}, {"q_bias", a + "q.b"}, {"k_proj", a + "k"}, {"k_bias", a + "k.b"}, {"q_norm", a + "q.norm"},
+                        {"k_norm", a + "k.norm"}, {"rel_bias", a + "rel"}, {"sink", a + "sink"}, {"o_proj", a + "o"}, {"o_bias", a + "o.b"}};
+        PartSpec right;
+        right.kind = "gated_delta_rule";
+        right.params["hidden_size"] = d;
+        right.params["num_heads"] = l.right.heads;
+        right.params["num_kv_heads"] = l.right.kv_heads;
+        right.params["key_dim"] = l.right.dim;
+        right.params["value_dim"] = l.right.vdim;
+        right.params["conv_taps"] = l.right.conv;
+        right.params["norm_eps"] = cfg.norm_eps;
+        right.tensors = {{"q_proj", b + "q"}, {"q_conv", b + "q.conv"}, {"k_proj", b + "k"}, {"k_conv", b + "k.conv"}, {"v_proj", b + "v"},
+                         {"v_conv", b + "v.conv"}, {"beta_proj", b + "b"}, {"a_log", b + "A_log"}, {"out_norm", b + "norm"}, {"a_proj", b + "a"},
+                         {"dt_bias", b + "dt_bias"}, {"gate_proj", b + "g"}, {"o_proj", b + "o"}};
+        LayerSpec layer;
+        layer.block = "parallel_prenorm";
+        layer.block_params["left_scale"] = l.left_scale;
+        layer.block_params["right_scale"] = l.right_scale;
+        layer.block_params["has_ffn"] = l.ff > 0;
+        layer.parts = {{"mixer_norm", norm(p + "norm1")}, {"left", left}, {"right", right}};
+        if (l.ff > 0) {
+            PartSpec ffn;
+            ffn.kind = "swiglu";
+            ffn.params["hidden_size"] = d;
+            ffn.params["intermediate_size"] = l.ff;
+            ffn.tensors = {{"gate_proj", p + "mlp.gate"}, {"up_proj", p + "mlp.up"}, {"down_proj", p + "mlp.down"}};
+            layer.parts.emplace_back("ffn_norm", norm(p + "norm2"));
+            layer.parts.emplace_back("feed_forward", ffn);
+        }
+        plan.layers.push_back(layer);
+    }
+    plan.embedding.kind = "token_embedding";
+    plan.embedding.params["vocab_size"] = cfg.vocab_size;
+    plan.embedding.params["hidden_size"] = d;
+    plan.embedding.tensors = {{"weight", "embed"}};
+    plan.final_norm = norm("final.norm");
+    plan.head.kind = "linear_head";
+    plan.head.params["vocab_size"] = cfg.vocab_size;
+    plan.head.params["hidden_size"] = d;
+    plan.head.params["scale"] = cfg.logit_scale;
+    plan.head.tensors = {{"weight", "head"}};
+    return plan;
+}
+
 // ------------------------------------------------------------------------------------ registry
 namespace {
 std::mutex g_arch_mutex;
@@ -249,6 +419,13 @@ void ensure_builtin_archs() {
         };
         q.plan = [](const Json& d) { return qwen3_plan(Qwen3Config::from_json(d, "config.json")); };
         archs()[q.name] = q;
+        Architecture k;
+        k.name = "Kazedra";
+        k.parse_config = [](const Json& d, const std::string& where) -> std::shared_ptr<ModelConfig> {
+            return std::make_shared<KazedraConfig>(KazedraConfig::from_json(d, where));
+        };
+        k.plan = [](const Json& d) { return kazedra_plan(KazedraConfig::from_json(d, "config.json")); };
+        archs()[k.name] = k;
     });
 }
 }  // namespace
@@ -288,9 +465,11 @@ const Architecture& architecture(const std::string& name) {
 const Architecture& architecture_of(const Json& config, const std::string& where) {
     if (!config.is_object()) bad(where + ": top level must be an object");
     const Json* a = config.find("architectures");
-    if (!a || !a->is_array() || a->size() == 0 || !(*a)[0].is_string())
-        bad(where + ": 'architectures' must be a list that names the model class");
-    return architecture((*a)[0].as_string());
+    if (a && a->is_array() && a->size() > 0 && (*a)[0].is_string()) return architecture((*a)[0].as_string());
+    // families that name themselves with a single string
+    const Json* one = config.find("architecture");
+    if (!a && one && one->is_string()) return architecture(one->as_string());
+    bad(where + ": 'architectures' must be a list that names the model class");
 }
 
 Json read_config_json(const std::string& path_or_text, std::string* where, std::string* folder) {

@@ -56,6 +56,36 @@ struct Qwen3Config : ModelConfig {
 
 ModelPlan qwen3_plan(const Qwen3Config& cfg);
 
+// Kazedra ("architecture": "Kazedra"): a pre-norm decoder whose layers run two mixers side by side on the same
+// normalised input, softmax attention with a sink and a bias by distance (left) and the gated delta rule (right),
+// added with fixed weights, followed by an optional gated feed-forward.  Its config.json lists the layers one by
+// one, each with its own sizes and constants; the keys are this family's own.
+struct KazedraConfig : ModelConfig {
+    struct Left {
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0, bias_max = 0, temp_every = 0;
+        double scale = 0, temp_coef = 0;
+    };
+    struct Right {
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0, conv = 0;
+    };
+    struct Layer {
+        std::string type;
+        Left left;
+        Right right;
+        double left_scale = 1, right_scale = 1;
+        int64_t ff = 0;            // 0 = the layer has no feed-forward
+    };
+    std::vector<Layer> layers;
+    double norm_eps = 1e-6, logit_scale = 1.0;
+
+    static KazedraConfig from_json(const Json& d, const std::string& where);
+    Json to_json() const override;
+};
+
+// Every size is in config.json except the rows of each layer's distance-bias table, which the checkpoint's tensor
+// gives; an optional model-wide `bias_buckets` key fixes them (random weights need it).
+ModelPlan kazedra_plan(const KazedraConfig& cfg);
+
 // ------------------------------------------------------------------------------------ registry
 struct Architecture {
     std::string name;

@@ -39,6 +39,29 @@ int imp_paged_attention_generic(void* out, int64_t out_stride, const void* q, in
                                 const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int Dh, int page_size,
                                 int num_pages, float scale, int window, int dtype, int* status, void* stream);
 
+int imp_paged_attention_generic_bias(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* k_cache,
+                                     const void* v_cache, const int* block_table, int bt_stride, const int* seq_of_token,
+                                     const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int Dh, int page_size,
+                                     int num_pages, float scale, int window, const float* bias, int n_dist, const float* sink,
+                                     int dtype, int* status, void* stream);
+int imp_proj_norm_kv_write(void* qk, int64_t row_stride, int n_tokens, int Hq, int Hkv, int Dh, const float* b_q, const float* b_k,
+                           const float* w_q, const float* w_k, float eps, float temp_coef, int temp_every, const int* positions,
+                           const int* seq_of_token, const int* block_table, int bt_stride, int n_seqs, void* k_cache,
+                           void* v_cache, int page_size, int num_pages, int act_dtype, int* status, void* stream);
+int imp_add_bias(void* x, int64_t stride, int n_rows, int n_cols, const float* bias, int dtype, void* stream);
+int imp_scaled_sum(void* out, const void* x, float a, const void* y, float b, const float* col_bias, float bias_scale, int n_rows,
+                   int n_cols, int dtype, void* stream);
+int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, int taps, const float* conv_state, const int* seq_of_token,
+                    const int* q_start, const int* slots, int n_tokens, int n_seqs, int G, int D, int H, int Dv, const float* a_log,
+                    const float* dt_bias, float* qn, float* kn, float* vc, float* beta, float* decay, int act_dtype, int* status,
+                    void* stream);
+int imp_gdr_conv_state(const void* proj, int64_t ld, float* conv_state, int taps, int C, const int* q_start, const int* slots,
+                       int n_seqs, int act_dtype, void* stream);
+int imp_gdr_scan(const float* qn, const float* kn, const float* vc, const float* beta, const float* decay, float* state, float* out,
+                 const int* q_start, const int* slots, int n_seqs, int G, int D, int H, int Dv, void* stream);
+int imp_gdr_output(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, float eps, int n_tokens, int H, int Dv,
+                   int act_dtype, void* stream);
+
 int imp_gemm_f32(float* C, int64_t ldc, const float* A, int64_t lda, const float* W, int64_t ldw, int M, int N, int K,
                  void* stream);
 int imp_gemm_bf16_plain(void* C, int64_t ldc, int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, int M,

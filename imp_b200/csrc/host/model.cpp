@@ -253,7 +253,8 @@ void DeviceModel::build(const std::vector<std::pair<std::string, Tensor>>& place
             parts.emplace_back(slot.name, factory_.build(slot.category, *ps, take(*ps)));
             mixers += slot.category == "mixer";
         }
-        if (mixers > 1) fail(IMP_ERROR_UNSUPPORTED, "block '" + layer.block + "': a block holds at most one mixer (one cache per layer)");
+        if (mixers > 1 && layer.cache_from >= 0)
+            fail(IMP_ERROR_UNSUPPORTED, "block '" + layer.block + "': a layer with several mixers cannot read another layer's cache");
         PartSpec bs;
         bs.kind = layer.block;
         bs.params = layer.block_params;
@@ -274,23 +275,27 @@ void DeviceModel::finish_build() {
         after_ok[(size_t)order_[j]] = after_ok[(size_t)order_[j]] && next_takes;
     }
     for (size_t i = 0; i < blocks_.size(); ++i) blocks_[i]->defer_pending = after_ok[i];
-    // Cache needs per run position, and which position's cache each position uses.
+    // Cache needs: one entry per mixer of every run position (one entry, possibly empty, for a position with a
+    // single mixer or none, so that models of one-mixer layers number their caches by run position), and which
+    // entry each position's first mixer uses.
     std::map<int, int> last_position_of_layer;
     for (size_t j = 0; j < order_.size(); ++j) {
         const int i = order_[j];
         const LayerSpec& layer = plan_.layers[(size_t)i];
         if (layer.cache_from < 0) {
-            CacheSpec spec;
+            std::vector<CacheSpec> specs;
             const PartClass& bc = part_class("block", layer.block);
             for (const auto& slot : bc.part_slots(layer.block_params))
                 if (slot.category == "mixer") {
                     const PartSpec* ps = layer.part(slot.name);
                     const PartClass& mc = part_class("mixer", ps->kind);
-                    if (mc.cache_spec) spec = mc.cache_spec(ps->params);
+                    specs.push_back(mc.cache_spec ? mc.cache_spec(ps->params) : CacheSpec());
                 }
-            cache_specs_.push_back(spec);
-            cache_position_.push_back((int)j);
-            last_position_of_layer[i] = (int)j;
+            if (specs.empty()) specs.push_back(CacheSpec());
+            cache_position_.push_back((int)cache_specs_.size());
+            cache_count_.push_back((int)specs.size());
+            cache_specs_.insert(cache_specs_.end(), specs.begin(), specs.end());
+            last_position_of_layer[i] = cache_position_.back();
         } else {
             auto it = last_position_of_layer.find(layer.cache_from);
             if (it == last_position_of_layer.end())
@@ -298,15 +303,22 @@ void DeviceModel::finish_build() {
                                                   ", which has not run before it in the run order");
             cache_specs_.push_back(CacheSpec());
             cache_position_.push_back(it->second);
+            cache_count_.push_back(1);
         }
     }
-    layer_caches_.assign(order_.size(), LayerCache());
+    cache_first_.clear();
+    int n_caches = 0;
+    for (size_t j = 0; j < order_.size(); ++j) {
+        cache_first_.push_back(n_caches);
+        n_caches += cache_count_[j];
+    }
+    layer_caches_.assign((size_t)n_caches, LayerCache());
     // The tilings the mixers want of a step, each distinct one once.
     graph_safe_ = embedding_->graph_safe() && final_norm_->graph_safe() && head_->graph_safe();
     for (Block* b : blocks_) {
         graph_safe_ = graph_safe_ && b->graph_safe();
         for (Part* p : b->parts()) graph_safe_ = graph_safe_ && p->graph_safe();
-        if (Mixer* m = b->mixer()) {
+        for (Mixer* m : b->mixers()) {
             m->tiling_ids.clear();
             for (const TilingSpec& t : m->tilings()) {
                 auto it = std::find(tilings_.begin(), tilings_.end(), t);
@@ -324,14 +336,22 @@ void DeviceModel::finish_build() {
 
 void DeviceModel::attach_cache(CacheManager* cache) {
     cache_ = cache;
+    // A position that owns its caches has them at consecutive entries of the cache manager; one that reads another
+    // layer's cache points at that layer's entry and writes nothing.
+    int own = 0;
     for (size_t j = 0; j < order_.size(); ++j) {
-        const int src = cache_position_[j];
-        LayerCache lc;
-        lc.view = cache->layer_view(src, rt_->dtype);
-        lc.view.writes = src == (int)j ? 1 : 0;
-        lc.group = cache->layer_ref()[(size_t)src].group;
-        layer_caches_[j] = lc;
+        const bool owns = plan_.layers[(size_t)order_[j]].cache_from < 0;
+        for (int m = 0; m < cache_count_[j]; ++m) {
+            const int src = cache_position_[j] + m;
+            LayerCache lc;
+            lc.view = cache->layer_view(src, rt_->dtype);
+            lc.view.writes = owns ? 1 : 0;
+            lc.group = cache->layer_ref()[(size_t)src].group;
+            layer_caches_[(size_t)cache_first_[j] + m] = lc;
+        }
+        own += owns ? cache_count_[j] : 1;
     }
+    (void)own;
 }
 
 Tensor DeviceModel::forward(Step& st) {
@@ -349,7 +369,9 @@ Tensor DeviceModel::forward(Step& st) {
     for (size_t j = 0; j < order_.size(); ++j) {
         rt_->arena->next_layer();
         st.layer = order_[j];
-        LayerCache* lc = layer_caches_[j].view.kind ? &layer_caches_[j] : nullptr;
+        // one mixer: its cache, or null when it has none; several: the array of their caches in slot order
+        LayerCache* lc = &layer_caches_[(size_t)cache_first_[j]];
+        if (cache_count_[j] == 1 && !lc->view.kind) lc = nullptr;
         pending = blocks_[(size_t)order_[j]]->forward(st, h, pending, lc);
     }
     st.layer = -1;

@@ -61,8 +61,8 @@ public:
     int64_t hidden_size() const { return plan_.hidden_size; }
     int64_t vocab_size() const { return plan_.vocab_size; }
     const std::vector<int>& order() const { return order_; }
-    const std::vector<CacheSpec>& cache_specs() const { return cache_specs_; }      // per run position
-    const std::vector<int>& cache_position() const { return cache_position_; }      // which position's cache each uses
+    const std::vector<CacheSpec>& cache_specs() const { return cache_specs_; }      // per mixer of every run position
+    const std::vector<int>& cache_position() const { return cache_position_; }      // which entry of cache_specs each position's first mixer uses
     const std::vector<TilingSpec>& tilings() const { return tilings_; }             // what the step function must fill
     bool graph_safe() const { return graph_safe_; }
     size_t weight_bytes() const { return store_.bytes(); }
@@ -84,7 +84,7 @@ private:
     std::vector<Block*> blocks_;
     Norm* final_norm_ = nullptr;
     Head* head_ = nullptr;
-    std::vector<int> order_, cache_position_;
+    std::vector<int> order_, cache_position_, cache_count_, cache_first_;
     std::vector<CacheSpec> cache_specs_;
     std::vector<LayerCache> layer_caches_;
     std::vector<TilingSpec> tilings_;

@@ -60,8 +60,15 @@ std::vector<TilingSpec> attention_tilings();
 // kernel (fixed reduction order per token).  bfloat16: the split-key decode kernel when every sequence
 // brings one token, else the tiled prefill kernels (tensor-memory kernel for long portions where the
 // head and page sizes allow it).  `tiling_ids`: where Step::tiles holds the three tilings above.
+// `extras`: a score bias by distance, bias [hq, n_dist] (score of key j for a query at p += bias[h][min(p - j,
+// n_dist - 1)]), and a sink per query head (exp(sink[h]) joins the softmax denominator); either may be null.
+struct AttentionExtras {
+    const float* bias = nullptr;   // float32 [hq, n_dist]
+    int n_dist = 0;
+    const float* sink = nullptr;   // float32 [hq]
+};
 void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
-                     const std::vector<int>& tiling_ids);
+                     const std::vector<int>& tiling_ids, const AttentionExtras* extras = nullptr);
 
 // The decode step from the raw rows of the q,k,v product: per-head norm and rotation of q and of the
 // new key happen inside the attention kernel, which writes the new key and value into their pages.

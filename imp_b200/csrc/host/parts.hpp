@@ -163,6 +163,12 @@ struct Block : Part {
     bool defer_pending = false;                          // set by the model: the pending it returns may be unsummed
     virtual bool takes_split_sum() const { return false; }   // the pending it is given may be unsummed
     virtual Mixer* mixer() const { return nullptr; }     // the part that owns this layer's cache, if any
+    // A block with several mixers names them in the order of its mixer slots; each owns a cache, and forward()
+    // gets them as an array in that order.
+    virtual std::vector<Mixer*> mixers() const {
+        Mixer* m = mixer();
+        return m ? std::vector<Mixer*>{m} : std::vector<Mixer*>{};
+    }
     virtual std::vector<Part*> parts() const = 0;
     virtual Branch forward(Step& st, Tensor h, const Branch& pending, LayerCache* cache) = 0;
     void call(Step& st, ImpCall& c) override;
@@ -227,6 +233,7 @@ void unregister_part_class(const std::string& category, const std::string& kind)
 const PartClass& part_class(const std::string& category, const std::string& kind);   // throws, listing known kinds
 std::vector<std::string> known_parts(const std::string& category);
 void ensure_builtin_parts();   // registers the library's own kinds once
+void register_mixer_parts();    // parts_mixers.cpp: the kinds beyond plain attention (called by ensure_builtin_parts)
 
 // Builds parts and owns them.  Parts without tensors are shared between equal specs.
 class PartFactory {

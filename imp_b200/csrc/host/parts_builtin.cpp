@@ -5,6 +5,7 @@
 #include <cmath>
 #include <mutex>
 
+#include "kernels.h"
 #include "ops.hpp"
 #include "parts.hpp"
 
@@ -298,11 +299,12 @@ struct TokenEmbedding : Embedding {
     }
 };
 
-// logits = x W^T in 32-bit (src/graph/executor_forward.cu:2953, 3075).  params: vocab_size, hidden_size.
-// The weight may be the embedding's own tensor.
+// logits = scale * x W^T in 32-bit (src/graph/executor_forward.cu:2953, 3075).  params: vocab_size, hidden_size,
+// scale (default 1).  The weight may be the embedding's own tensor.
 struct LinearHead : Head {
     Tensor weight;
-    explicit LinearHead(BuildArgs& a) : weight(a.tensor("weight")) {}
+    float scale;
+    explicit LinearHead(BuildArgs& a) : weight(a.tensor("weight")), scale((float)a.params.get_double("scale", 1.0)) {}
     static TensorSpecs specs(const Json& p) {
         TensorSpecs s;
         s.emplace_back("weight", TensorSpec{{need_int(p, "vocab_size", "linear_head"), need_int(p, "hidden_size", "linear_head")}});
@@ -311,6 +313,11 @@ struct LinearHead : Head {
     Tensor forward(Step& st, Tensor x) override {
         Tensor out = st.rt->empty(rows(x), rows(weight), F32, /*step=*/true);
         linear(*st.rt, out, x, weight);
+        if (scale != 1.f) {
+            ++st.rt->launches;
+            check_launch(imp_scaled_sum(out.data, out.data, scale, nullptr, 0.f, nullptr, 0.f, (int)rows(out), (int)cols(out), F32, st.rt->stream),
+                         "scaled_sum");
+        }
         return out;
     }
 };
@@ -344,6 +351,7 @@ void ensure_builtin_parts() {
         register_part_class("block", "prenorm", block, true);
         register_part_class("embedding", "token_embedding", simple_class<TokenEmbedding>(&TokenEmbedding::specs), true);
         register_part_class("head", "linear_head", simple_class<LinearHead>(&LinearHead::specs), true);
+        register_mixer_parts();
     });
 }
 

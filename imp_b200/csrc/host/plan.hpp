@@ -20,7 +20,7 @@ namespace imp {
 
 // What a part expects of one checkpoint tensor.
 struct TensorSpec {
-    std::vector<int64_t> shape;
+    std::vector<int64_t> shape;    // -1: any size (the checkpoint's tensor decides; the part reads it from there)
     std::string role = "matrix";   // "matrix" | "norm" | "vector" | "int_table"
     std::string init = "normal";   // random-weights rule: "normal" | "one_plus_normal" | "zeros" | "arange_mod"
     bool optional = false;

@@ -179,7 +179,11 @@ void check_checkpoint(const std::vector<std::pair<std::string, TensorSpec>>& exp
             if (!e.second.optional) missing.push_back(e.first);
             continue;
         }
-        if (it->second.shape != e.second.shape)
+        // a dimension given as -1 is the checkpoint's to choose (the part reads it from the tensor)
+        bool shape_ok = it->second.shape.size() == e.second.shape.size();
+        for (size_t i = 0; shape_ok && i < e.second.shape.size(); ++i)
+            shape_ok = e.second.shape[i] < 0 || e.second.shape[i] == it->second.shape[i];
+        if (!shape_ok)
             wrong_shape.push_back(e.first + ": expected " + shape_str(e.second.shape) + ", found " + shape_str(it->second.shape));
         const std::string& dt = it->second.dtype;
         const bool floating = dt == "F32" || dt == "BF16" || dt == "F16" || dt == "F64";
@@ -357,6 +361,8 @@ Tensor random_device_tensor(const std::string& name, const TensorSpec& spec, int
                             const std::string& stored_dtype, int compute_dtype, WeightStore& store, cudaStream_t stream) {
     // values are made in the stored type's precision first, as a checkpoint would hold them
     const int target = device_dtype(stored_dtype, spec.role, compute_dtype);
+    for (int64_t d : spec.shape)
+        if (d < 0) fail(IMP_ERROR_INVALID_MODEL, "tensor '" + name + "' has a size that only a checkpoint gives; random weights need it in the configuration");
     Tensor dst = store.alloc(target, spec.shape);
     const int64_t n = numel(dst);
     if (n == 0) return dst;
@@ -386,6 +392,8 @@ void write_random_model(const Json& config, const ModelPlan& plan, const std::st
         HostTensor t;
         t.name = e.first;
         t.shape = e.second.shape;
+        for (int64_t d : t.shape)
+            if (d < 0) fail(IMP_ERROR_INVALID_MODEL, "tensor '" + e.first + "' has a size that only a checkpoint gives; random weights need it in the configuration");
         const int64_t n = e.second.numel();
         const bool ints = e.second.role == "int_table";
         t.dtype = ints ? "I32" : bf16 ? "BF16" : "F32";

@@ -192,9 +192,10 @@ class Model:
 
     @property
     def config(self) -> ModelConfig:
+        from ..config.model_config import architecture_name
         from ..config.registry import config_class_of
         d = json.loads(capi.text(capi.load().imp_model_config_json(self._h)))
-        return config_class_of(d["architectures"][0])(d)
+        return config_class_of(architecture_name(d))(d)
 
     def plan_json(self) -> Dict[str, Any]:
         return json.loads(capi.text(capi.load().imp_model_plan_json(self._h)))
