@@ -26,6 +26,7 @@ Other runs, each printing its own JSON line:
     python bench.py --only mixed [--batch B] [--chunk C] [--context X]     B sequences decoding beside a prompt's portions
     IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE python bench.py --only timeline [--batch B] [--context C] [--workload 0.6b|14b]   (a table, not JSON)
     python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
+    python bench.py --arch kazedra [--layers N] [--batch B]    Kazedra beside Qwen3 at equal sizes: prefill and decode
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
 """
@@ -700,6 +701,61 @@ def run_workload(args):
     return 0
 
 
+# ------------------------------------------------------------------------------ another architecture
+# Shapes that resemble real models' layers (width, query / kv heads of 128, inner size), few layers, vocabulary 32,768.
+ARCH_SHAPES = {"1b": (1024, 16, 8, 3072), "8b": (4096, 32, 8, 12288)}
+
+
+def kazedra_config(width, heads, kv_heads, ff, layers, vocab):
+    lay = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "bias_max": 2048, "scale": 128 ** -0.5,
+                              "q_temp": {"coef": 0.1, "every": 64}},
+                     "right": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4},
+                     "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Kazedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0, "bias_buckets": 32,
+            "layers": [lay] * layers, "max_positions": 8192}
+
+
+def run_arch(args):
+    """Prefill and decode of Kazedra beside the Qwen3 decoder at equal sizes (random weights): a 2,048-token prompt whole
+    and in 512-token portions, and decode steps of `--batch` sequences at context 2,048, device time between CUDA events."""
+    peaks, peak_src = read_peaks()
+    layers, vocab, B = args.layers or 4, 32768, args.batch
+    out = {"arch": "kazedra", "beside": "qwen3", "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
+    with Clocks() as clocks:
+        for name, (width, heads, kv, ff) in ARCH_SHAPES.items():
+            models = {"kazedra": kazedra_config(width, heads, kv, ff, layers, vocab),
+                      "qwen3": dict(MODEL, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
+                                    intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)}
+            row = {}
+            for label, cfgd in models.items():
+                rng = random.Random(0)
+                eng, _ = make_engine(cfgd, args, B, 4096)
+                whole = time_prefill(eng, rng, vocab, 2048, 0, reps=5)
+                cut = time_prefill(eng, rng, vocab, 2048, 512, reps=5)
+                reqs = start_decoding(eng, rng, vocab, B, 2048, args.steps + args.warmup + 16)
+                for _ in range(args.warmup):
+                    eng.step()
+                before = eng.info()
+                ms = timed_steps(eng, args.steps, B) / args.steps
+                info = eng.info()
+                stop(eng, reqs)
+                row[label] = {"prefill_2048_ms": spread(whole), "prefill_tok_s": round(2048e3 / statistics.median(whole)),
+                              "prefill_512_portions_ms": spread(cut), "decode_ms_per_step": round(ms, 4),
+                              "decode_tok_s": round(B * 1e3 / ms), "weight_bytes": info["model"]["weight_bytes"],
+                              "decode_weight_gbs": round(info["model"]["weight_bytes"] / ms / 1e6, 1),
+                              "launches_per_decode_step": (info["launches"] - before["launches"]) / args.steps,
+                              "graph_replays": info["graph_replays"] - before["graph_replays"], "fallback_calls": info["fallback_calls"]}
+                del eng
+            row["prefill_ratio"] = round(statistics.median([row["kazedra"]["prefill_2048_ms"]["median"]]) / row["qwen3"]["prefill_2048_ms"]["median"], 3)
+            row["decode_ratio"] = round(row["kazedra"]["decode_ms_per_step"] / row["qwen3"]["decode_ms_per_step"], 3)
+            out["shapes"][name] = row
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args):
     """The one offline install the contract describes is attempted once (it cannot succeed: the reference is a
     CMake C++/CUDA project without setup.py or pyproject.toml, it needs CUDA >= 13.1 where this image has 12.9,
@@ -732,6 +788,8 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "mixed"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
+    ap.add_argument("--arch", default="", choices=["", "kazedra"],
+                    help="prefill and decode of this architecture beside the Qwen3 decoder at equal sizes (not the default workload)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
     ap.add_argument("--quick", action="store_true", help="skip the 2,048-step protocol runs and the yardsticks")
     ap.add_argument("--context", type=int, default=0,
@@ -754,6 +812,8 @@ def main():
         return run_mixed(args)
     if args.workload:
         return run_workload(args)
+    if args.arch:
+        return run_arch(args)
     return run_ours(args)
 
 

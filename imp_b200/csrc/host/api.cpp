@@ -579,7 +579,9 @@ IMP_EXPORT ImpError imp_bench_build_part(ImpBench b, const char* category, const
                 role = s.second.role;
                 known = true;
                 std::vector<int64_t> shape(tensors[i].shape, tensors[i].shape + tensors[i].ndim);
-                if (shape != s.second.shape)
+                bool fits = shape.size() == s.second.shape.size();
+                for (size_t k = 0; fits && k < shape.size(); ++k) fits = s.second.shape[k] < 0 || s.second.shape[k] == shape[k];   // -1: any size
+                if (!fits)
                     fail(IMP_ERROR_INVALID_ARG, std::string("tensor '") + names[i] + "' has shape " + shape_string(tensors[i]) + ", not what the part expects");
             }
         if (!known) fail(IMP_ERROR_INVALID_ARG, std::string(category) + " '" + spec.kind + "' has no tensor '" + names[i] + "'");

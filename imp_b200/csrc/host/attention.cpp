@@ -32,8 +32,16 @@ using PrefillFn = int (*)(void*, int64_t, const void*, int64_t, const void*, con
 using PrefillTcFn = int (*)(void*, int64_t, const void*, int64_t, int, const void*, const void*, const int*, int, const int*,
                             const int*, const int*, const int*, int, int, int, int, int, int, float, int, int*, void*);
 
+using DecodeBiasFn = int (*)(void*, int64_t, const void*, int64_t, const void*, const void*, const int*, int, const int*, const int*,
+                             int, int, int, int, int, int, float, int, int, float*, const float*, int, const float*, int*, void*);
+using PrefillBiasFn = int (*)(void*, int64_t, const void*, int64_t, const void*, const void*, const int*, int, const int*,
+                              const int*, const int*, const int*, int, int, int, int, int, int, float, int, const float*, int,
+                              const float*, int*, void*);
+
 struct MmaVariant {
     void* handle = nullptr;
+    DecodeBiasFn decode_bias = nullptr;
+    PrefillBiasFn prefill_bias = nullptr;
     const char* (*last_error)() = nullptr;
     int64_t (*scratch_floats)(int, int, int) = nullptr;
     DecodeFn decode = nullptr;
@@ -116,6 +124,8 @@ MmaVariant& mma_variant(int head_dim) {
     bind(v.handle, "imp_attn_decode", v.decode, path);
     bind(v.handle, "imp_attn_decode_fused", v.decode_fused, path);
     bind(v.handle, "imp_attn_prefill", v.prefill, path);
+    bind(v.handle, "imp_attn_decode_bias", v.decode_bias, path);
+    bind(v.handle, "imp_attn_prefill_bias", v.prefill_bias, path);
     return g_mma[head_dim] = v;
 }
 
@@ -283,6 +293,56 @@ static bool prefill_tc_supported(const Tensor& q, const Tensor& out, const Atten
     return tc_variant(g.dh).supported(q.stride0, out.stride0, c.page_size) != 0;
 }
 
+// Attention with a score bias by distance and a sink on the tensor-core kernels: the split-key decode kernel that reads
+// the pages directly for the sequences that bring one token (a decode step, or the leading rows of a mixed step), the
+// 32-token tiles for the rest.  False, with nothing done, where those kernels do not apply (float32, head sizes that are
+// no multiple of 16, rows that do not start on 16 bytes, no tables in the log2 domain, IMP_B200_ATTN_BIAS=generic).
+static bool bias_attention_mma(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
+                               const std::vector<int>& tiling_ids, const AttentionExtras& ex) {
+    Runtime& rt = *st.rt;
+    static const bool generic_only = env_string("IMP_B200_ATTN_BIAS", "mma") == "generic";
+    const ImpCacheView& c = cache.view;
+    if (generic_only || rt.is_f32() || q.dtype != BF16 || g.dh % 16 || g.dh > 256) return false;
+    if ((ex.bias && !ex.bias_l2) || (ex.sink && !ex.sink_l2)) return false;
+    if (q.stride0 % 8 || out.stride0 % 2 || (uintptr_t)q.data % 16 || (uintptr_t)c.k_pages % 16 || (uintptr_t)c.v_pages % 16) return false;
+    if (!st.decode_only() && tiling_ids.size() != 5) return false;
+    MmaVariant& lib = mma_variant(g.dh);
+    auto decode = [&](Tensor o, const Tensor& qq) {
+        const int T = (int)rows(qq), G = g.hq / g.hkv;
+        // splits until every SM holds about three CTAs, none shorter than 64 keys of the typical context
+        const int base = std::max(1, T * g.hkv * ((G + 15) / 16));
+        int n_splits = std::max(1, std::min(DECODE_MAX_SPLITS, rt.sm_count * 3 / base));
+        if (st.context > 0) n_splits = std::max(1, std::min(n_splits, st.context / 64));
+        const int64_t n_floats = lib.scratch_floats(T, g.hq, n_splits);
+        float* scratch = n_floats ? (float*)rt.arena->alloc((size_t)n_floats * 4) : nullptr;
+        check_variant(rt,
+                      lib.decode_bias(o.data, o.stride0, qq.data, qq.stride0, c.k_pages, c.v_pages, c.block_table, c.bt_stride,
+                                      st.view.seq_of_token, st.view.positions, T, st.B(), g.hq, g.hkv, c.page_size, c.num_pages, g.scale,
+                                      g.window, n_splits, scratch, ex.bias_l2, ex.n_dist, ex.sink_l2, rt.status, rt.stream),
+                      "attention decode (bias, sink)", lib.last_error);
+        if (n_splits > 1) ++rt.launches;
+    };
+    if (st.decode_only()) {
+        decode(out, q);
+        return true;
+    }
+    int n_single = 0;
+    while (n_single < st.B() && st.q_lens[(size_t)n_single] == 1) ++n_single;
+    bool singles = n_single > 0;
+    for (int i = n_single; singles && i < st.B(); ++i)
+        if (st.q_lens[(size_t)i] == 1) singles = false;
+    if (singles) decode(first_rows(out, n_single), first_rows(q, n_single));
+    const Tiles& tiles = st.tiles.at((size_t)tiling_ids[singles ? 3 : 0]);
+    if (tiles.count)
+        check_variant(rt,
+                      lib.prefill_bias(out.data, out.stride0, q.data, q.stride0, c.k_pages, c.v_pages, c.block_table, c.bt_stride,
+                                       st.view.seq_of_token, st.view.positions, tiles.tok0, tiles.rows, tiles.count, st.B(), g.hq, g.hkv,
+                                       c.page_size, c.num_pages, g.scale, g.window, ex.bias_l2, ex.n_dist, ex.sink_l2, rt.status,
+                                       rt.stream),
+                      "attention prefill (bias, sink)", lib.last_error);
+    return true;
+}
+
 void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
                      const std::vector<int>& tiling_ids, const AttentionExtras* extras) {
     Runtime& rt = *st.rt;
@@ -290,6 +350,7 @@ void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeome
     const ImpCacheView& c = cache.view;
     need(rows(out) == rows(q) && out.dtype == q.dtype, "attention: out and q must agree");
     if (extras && (extras->bias || extras->sink)) {
+        if (bias_attention_mma(st, out, q, g, cache, tiling_ids, *extras)) return;
         ++rt.launches;
         check_launch(imp_paged_attention_generic_bias(out.data, out.stride0, q.data, q.stride0, c.k_pages, c.v_pages, c.block_table,
                                                       c.bt_stride, st.view.seq_of_token, st.view.positions, (int)rows(q), st.B(),

@@ -66,6 +66,9 @@ struct AttentionExtras {
     const float* bias = nullptr;   // float32 [hq, n_dist]
     int n_dist = 0;
     const float* sink = nullptr;   // float32 [hq]
+    // the same tables times log2(e), for the kernels that exponentiate with base 2 (null: only the plain kernel runs)
+    const float* bias_l2 = nullptr;
+    const float* sink_l2 = nullptr;
 };
 void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
                      const std::vector<int>& tiling_ids, const AttentionExtras* extras = nullptr);

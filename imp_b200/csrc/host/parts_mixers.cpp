@@ -49,6 +49,7 @@ struct SinkBiasAttention : Mixer {
     AttentionGeometry g;
     Tensor w_qk, w_o;
     Tensor b_q, b_k, b_o, n_q, n_k, sink, bias_by_distance;   // float32
+    Tensor sink_l2, bias_l2;                                   // the last two times log2(e), for kernels that use 2^x
     float eps, temp_coef;
     int temp_every, n_dist;
 
@@ -117,6 +118,15 @@ struct SinkBiasAttention : Mixer {
         bias_by_distance = a.store->alloc(F32, {g.hq, n_dist});
         IMP_CUDA(cudaMemcpyAsync(bias_by_distance.data, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, rt.stream));
         IMP_CUDA(cudaStreamSynchronize(rt.stream));
+        const double log2e = 1.4426950408889634;
+        std::vector<float> sk = to_host_f32(rt, *a.store, sink);
+        for (float& v : tab) v = (float)((double)v * log2e);
+        for (float& v : sk) v = (float)((double)v * log2e);
+        bias_l2 = a.store->alloc(F32, {g.hq, n_dist});
+        sink_l2 = a.store->alloc(F32, {g.hq});
+        IMP_CUDA(cudaMemcpyAsync(bias_l2.data, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, rt.stream));
+        IMP_CUDA(cudaMemcpyAsync(sink_l2.data, sk.data(), sk.size() * 4, cudaMemcpyHostToDevice, rt.stream));
+        IMP_CUDA(cudaStreamSynchronize(rt.stream));
         for (const char* n : {"q_proj", "k_proj", "q_bias", "k_bias", "o_bias", "q_norm", "k_norm", "sink", "rel_bias"}) a.drop(n);
     }
 
@@ -141,6 +151,8 @@ struct SinkBiasAttention : Mixer {
         ex.bias = (const float*)bias_by_distance.data;
         ex.n_dist = n_dist;
         ex.sink = (const float*)sink.data;
+        ex.bias_l2 = (const float*)bias_l2.data;
+        ex.sink_l2 = (const float*)sink_l2.data;
         paged_attention(st, attn, col_slice(qk, 0, qd), g, *cache, tiling_ids, &ex);
         Tensor out = rt.empty(T, rows(w_o));
         linear(rt, out, attn, w_o);

@@ -85,6 +85,16 @@ struct RowInfo {
     int first;   // first key position (window), 0 without a window
 };
 
+// Optional additions to the scores (mixers that are not plain softmax attention), both in the log2 domain, that is
+// multiplied by log2(e) by the caller: a bias by distance and query head, bias_l2[head][min(p - j, n_dist - 1)], added
+// to the scaled score of key j for a query at position p; and one more term of the softmax denominator per head,
+// 2^sink_l2[head], which has no key and no value.
+struct ScoreExtras {
+    const float* bias_l2;   // [Hq, n_dist] or null
+    int n_dist;
+    const float* sink_l2;   // [Hq] or null
+};
+
 struct TileState {
     float o[NTILES][4];   // [tile][c0,c1 (row g), c2,c3 (row g+8)]
     float m[2], l[2];     // running max (log2 domain) and lane-partial sum for rows g and g+8
@@ -163,10 +173,11 @@ __device__ __forceinline__ void dec_mma(float (&acc)[2 * NR], uint32_t a0, uint3
 }
 
 // Scores, softmax update and P V for the 16 keys j0 .. j0+15 whose loads `L` holds.
-template <int NR>
+template <int NR, bool BIAS = false>
 __device__ __forceinline__ void dec_compute(DecState<NR>& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
                                             const DecLoads& L, const __nv_bfloat16* __restrict__ vc, int j0,
-                                            float scale_log2, int lane) {
+                                            float scale_log2, int lane, const float* bias_r0 = nullptr,
+                                            const float* bias_r1 = nullptr, int n_dist = 0) {
     const int g = lane >> 2, t = lane & 3;
     // the value rows are requested first: they travel while the scores are computed
     uint4 vr[VBlocks::N64 > 0 ? VBlocks::N64 : 1][4];
@@ -189,9 +200,11 @@ __device__ __forceinline__ void dec_compute(DecState<NR>& st, const uint32_t (&q
     for (int r = 0; r < NR; ++r) {
         float v[4] = {s0[2 * r] * scale_log2, s0[2 * r + 1] * scale_log2, s1[2 * r] * scale_log2, s1[2 * r + 1] * scale_log2};
         float mx = -INFINITY;
+        const float* bias_r = BIAS ? (r == 0 ? bias_r0 : bias_r1) : nullptr;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int j = j0 + 8 * (e >> 1) + 2 * t + (e & 1);
+            if (BIAS && bias_r) v[e] += bias_r[min(max(rows[r].limit - j, 0), n_dist - 1)];
             if (j > rows[r].limit || j < rows[r].first) v[e] = -INFINITY;
             mx = fmaxf(mx, v[e]);
         }
@@ -335,10 +348,15 @@ __device__ __forceinline__ void load_k_frags(uint32_t (&f)[KSTEPS][2], const uns
 // of all 32 keys first, one softmax update (one rescale of the accumulator), then two P V steps.
 // Scores stay unscaled; the scale (times log2 e) enters as the factor of a fused multiply-add in
 // front of ex2.  `need_mask` (warp-uniform) is false when every key is visible to every row.
+// BIAS: the scores are scaled first and the distance bias of the warp's head (`bias_h`, log2 domain) is added; what
+// follows then works on scaled scores (factor 1).
+template <bool BIAS = false>
 __device__ __forceinline__ void process_stage32(TileState& st, const uint32_t (&qa)[KSTEPS][4], const RowInfo (&rows)[2],
                                                 const unsigned char* __restrict__ ksm, const unsigned char* __restrict__ vsm,
-                                                int j0, float scale_log2, bool need_mask, int lane) {
+                                                int j0, float scale_log2_in, bool need_mask, int lane,
+                                                const float* __restrict__ bias_h = nullptr, int n_dist = 0) {
     const int g = lane >> 2, t = lane & 3;
+    const float scale_log2 = BIAS ? 1.f : scale_log2_in;
     float s[4][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -363,6 +381,17 @@ __device__ __forceinline__ void process_stage32(TileState& st, const uint32_t (&
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
             mma_16816(s[nt], qa[KSTEPS - 1][0], qa[KSTEPS - 1][1], qa[KSTEPS - 1][2], qa[KSTEPS - 1][3], v[nt].x, v[nt].y);
+    }
+    if (BIAS) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int dist = min(max(rows[r].limit - (j0 + 8 * nt + 2 * t + e), 0), n_dist - 1);
+                    s[nt][2 * r + e] = fmaf(s[nt][2 * r + e], scale_log2_in, bias_h ? bias_h[dist] : 0.f);
+                }
     }
     if (need_mask) {
 #pragma unroll
@@ -493,13 +522,13 @@ __device__ __forceinline__ void load_q(uint32_t (&qa)[KSTEPS][4], const __nv_bfl
 // grid (n_splits, Hkv * tiles_per_group, n_tokens), block 128.  Each warp takes every fourth 16-key
 // step of the CTA's split; several CTAs per SM keep enough loads in flight.
 // part_o: [n_tokens, Hq, n_splits, DH] float, part_ml: [n_tokens, Hq, n_splits, 2] float (used when n_splits > 1).
-template <int NR>
+template <int NR, bool BIAS = false>
 __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kernel(
     __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n_seqs, int Hq,
     int Hkv, int P, int num_pages, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int* status) {
+    float* __restrict__ part_ml, int* status, ScoreExtras ex) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float smem[];   // (WARPS-1) x (NTILES*2*NR + 2*NR) x 32 floats
@@ -535,6 +564,14 @@ __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kerne
         rows[r].first = first;
         qrow[r] = used ? q + (int64_t)tok * q_stride + (int64_t)(hk * G + hr) * DH : nullptr;
     }
+    const float* bias_r[2] = {nullptr, nullptr};
+    if (BIAS && ex.bias_l2) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int hr = row0 + g + 8 * r;
+            if (r < NR && hr < G) bias_r[r] = ex.bias_l2 + (int64_t)(hk * G + hr) * ex.n_dist;
+        }
+    }
     int s = step_lo + warp;
     uint32_t qa[KSTEPS][4];
     load_q(qa, qrow[0], qrow[1], t4);
@@ -548,7 +585,7 @@ __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kerne
     for (; s < step_hi; s += WARPS) {
         DecLoads cur;
         dec_fetch(cur, kc, bt, P, Hkv, hk, num_pages, first16 + 16 * s, first, pos, lane, status);
-        dec_compute<NR>(st, qa, rows, cur, vc, first16 + 16 * s, scale_log2, lane);
+        dec_compute<NR, BIAS>(st, qa, rows, cur, vc, first16 + 16 * s, scale_log2, lane, bias_r[0], bias_r[1], ex.n_dist);
     }
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
@@ -597,6 +634,15 @@ __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kerne
         if (hr >= G) continue;
         const int head = hk * G + hr;
         if (n_splits == 1) {
+            if (BIAS && ex.sink_l2) {
+                // the sink: one more term of the denominator, against the running maximum
+                const float sk = ex.sink_l2[head];
+                const float m_new = fmaxf(st.m[r], sk);
+                const float c = exp2f(st.m[r] - m_new);            // st.m = -inf -> 0
+                st.l[r] = st.l[r] * c + exp2f(sk - m_new);
+#pragma unroll
+                for (int i = 0; i < NTILES; ++i) { st.o[i][2 * r] *= c; st.o[i][2 * r + 1] *= c; }
+            }
             const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
             __nv_bfloat16* o = out + (int64_t)tok * out_stride + (int64_t)head * DH;
 #pragma unroll
@@ -627,7 +673,8 @@ constexpr int MERGE_MAX_SPLITS = 256;
 
 __global__ void __launch_bounds__(128) attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t out_stride,
                                                          const float* __restrict__ part_o,
-                                                         const float* __restrict__ part_ml, int Hq, int n_splits) {
+                                                         const float* __restrict__ part_ml, int Hq, int n_splits,
+                                                         const float* __restrict__ sink_l2) {
     IMP_TL_BEGIN(7)
     pdl_wait();
     IMP_TL_WAITED()
@@ -644,7 +691,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(__nv_bfloat16* __restri
         for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, ml[2 * s]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        float L = 0.f;
+        if (sink_l2) M = fmaxf(M, sink_l2[head]);          // the sink is one more term of the denominator
+        float L = sink_l2 ? exp2f(sink_l2[head] - M) : 0.f;
         for (int s0 = 0; s0 < n_splits; s0 += 32) {        // fixed order: chunks of 32 splits, tree inside a chunk
             const int s = s0 + lane;
             float w = 0.f, l = 0.f;
@@ -1358,22 +1406,22 @@ static int launch_decode_tma(dim3 grid, cudaStream_t s, void* out, int64_t out_s
     return 0;
 }
 
-template <int NR>
+template <int NR, bool BIAS = false>
 static int launch_decode(dim3 grid, cudaStream_t s, void* out, int64_t out_stride, const void* q, int64_t q_stride,
                          const void* kc, const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
                          const int* positions, int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2,
-                         int window, int n_splits, float* part_o, float* part_ml, int* status) {
+                         int window, int n_splits, float* part_o, float* part_ml, int* status, ScoreExtras ex = ScoreExtras{}) {
     constexpr int SMEM = (WARPS - 1) * (NTILES * 2 * NR + 2 * NR) * 32 * (int)sizeof(float);   // warp merge buffer
     static bool attr_set = false;
     if (!attr_set && SMEM > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NR, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
-    cudaError_t e = imp_launch(attn_decode_kernel<NR>, grid, dim3(WARPS * 32), (size_t)SMEM, s, (__nv_bfloat16*)out, out_stride,
+    cudaError_t e = imp_launch(attn_decode_kernel<NR, BIAS>, grid, dim3(WARPS * 32), (size_t)SMEM, s, (__nv_bfloat16*)out, out_stride,
                                (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
                                block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, num_pages, scale_log2,
-                               window, n_splits, part_o, part_ml, status);
+                               window, n_splits, part_o, part_ml, status, ex);
     if (e != cudaSuccess) { imp_set_error("imp_attn_decode: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1418,7 +1466,7 @@ static int attn_decode_impl(void* out, int64_t out_stride, const void* q, int64_
 #undef DEC_ARGS
     if (n_splits > 1 && !merged) {
         imp_launch(attn_merge_kernel, dim3(n_tokens * Hq), dim3(128), 0, s, (__nv_bfloat16*)out, out_stride,
-                   (const float*)part_o, (const float*)part_ml, Hq, n_splits);
+                   (const float*)part_o, (const float*)part_ml, Hq, n_splits, (const float*)nullptr);
     }
     IMP_RETURN_LAUNCH();
 }
@@ -1429,6 +1477,35 @@ IMP_API int imp_attn_decode(void* out, int64_t out_stride, const void* q, int64_
                             float scale, int window, int n_splits, float* scratch, int* status, void* stream) {
     return attn_decode_impl(out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_tokens,
                             n_seqs, Hq, Hkv, P, num_pages, scale, window, n_splits, scratch, status, stream, DecFused{});
+}
+
+// Decode with a score bias by distance and a sink (see ScoreExtras; either table may be null): the kernel that reads
+// keys straight from the pages, at any page size.  The splits' merge adds the sink's term.
+IMP_API int imp_attn_decode_bias(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
+                                 const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                                 const int* positions, int n_tokens, int n_seqs, int Hq, int Hkv, int P, int num_pages,
+                                 float scale, int window, int n_splits, float* scratch, const float* bias_l2, int n_dist,
+                                 const float* sink_l2, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
+    IMP_CHECK_ARG(seq_of_token && positions, "imp_attn_decode_bias: null pointer");
+    IMP_CHECK_ARG(!bias_l2 || n_dist > 0, "imp_attn_decode_bias: a bias table needs at least one distance");
+    IMP_CHECK_ARG(n_splits >= 1 && n_splits <= MERGE_MAX_SPLITS && (n_splits == 1 || scratch) && n_tokens <= 65535,
+                  "imp_attn_decode_bias: bad split count, scratch or token count");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int G = Hq / Hkv;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (int64_t)n_tokens * Hq * n_splits * DH : nullptr;
+    const ScoreExtras ex{bias_l2, n_dist, sink_l2};
+    dim3 grid(n_splits, Hkv * ((G + 15) / 16), n_tokens);
+#define DEC_ARGS grid, s, out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, n_seqs, Hq, Hkv, P, \
+                 num_pages, scale * 1.4426950408889634f, window, n_splits, part_o, part_ml, status, ex
+    if (int rc = (G <= 8) ? launch_decode<1, true>(DEC_ARGS) : launch_decode<2, true>(DEC_ARGS)) return rc;
+#undef DEC_ARGS
+    if (n_splits > 1)
+        imp_launch(attn_merge_kernel, dim3(n_tokens * Hq), dim3(128), 0, s, (__nv_bfloat16*)out, out_stride, (const float*)part_o,
+                   (const float*)part_ml, Hq, n_splits, sink_l2);
+    IMP_RETURN_LAUNCH();
 }
 
 // The decode step from the projection's raw rows: qkv [n_tokens, qkv_stride] holds q heads, k heads, v heads of
@@ -1462,13 +1539,13 @@ constexpr int PRE_KEYS = 32;
 constexpr int PRE_STAGES = 3;
 constexpr int PRE_SMEM_BYTES = PRE_STAGES * StageGeom<PRE_KEYS>::BYTES;
 
-template <int HPC>
+template <int HPC, bool BIAS = false>
 __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
     __nv_bfloat16* __restrict__ out, int64_t out_stride, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_seqs, int Hq, int Hkv, int P,
-    int num_pages, float scale_log2, int window, int* status) {
+    int num_pages, float scale_log2, int window, int* status, ScoreExtras ex) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -1524,6 +1601,7 @@ __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
     load_q(qa, qrow[0], qrow[1], t4);
     TileState st;
     tile_init(st);
+    const float* bias_h = (BIAS && ex.bias_l2 && warp_used) ? ex.bias_l2 + (int64_t)head * ex.n_dist : nullptr;
     for (int s = 0; s < n_stages; ++s) {
         cp_wait<PRE_STAGES - 2>();   // stage s has landed (this thread's part)
         __syncthreads();             // ... and everyone's; the slot of stage s-1 is free again
@@ -1538,7 +1616,7 @@ __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
         if (j0 <= my_last && j0 + PRE_KEYS - 1 >= my_first) {
             // every key of the stage visible to every row of the warp: no mask needed
             const bool need_mask = j0 + PRE_KEYS - 1 > my_lo_limit || j0 < my_hi_first;
-            process_stage32(st, qa, rows, ksm, vsm, j0, scale_log2, need_mask, lane);
+            process_stage32<BIAS>(st, qa, rows, ksm, vsm, j0, scale_log2, need_mask, lane, bias_h, ex.n_dist);
         }
     }
     cp_wait<0>();
@@ -1549,6 +1627,15 @@ __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
         const int rr = sub * 16 + g + 8 * r;
         if (rr >= n_rows) continue;
+        if (BIAS && ex.sink_l2) {
+            // the sink: one more term of the denominator (st.m holds scaled scores in the log2 domain here)
+            const float sk = ex.sink_l2[head];
+            const float m_new = fmaxf(st.m[r], sk);
+            const float c = exp2f(st.m[r] - m_new);                // st.m = -inf -> 0
+            st.l[r] = st.l[r] * c + exp2f(sk - m_new);
+#pragma unroll
+            for (int i = 0; i < NTILES; ++i) { st.o[i][2 * r] *= c; st.o[i][2 * r + 1] *= c; }
+        }
         const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
         __nv_bfloat16* o = out + (int64_t)(tok0 + rr) * out_stride + (int64_t)head * DH;
 #pragma unroll
@@ -1559,24 +1646,24 @@ __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
     }
 }
 
-template <int HPC>
+template <int HPC, bool BIAS = false>
 static int launch_prefill(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc, const void* vc,
                           const int* block_table, int bt_stride, const int* seq_of_token, const int* positions,
                           const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv, int P,
-                          int num_pages, float scale, int window, int* status, cudaStream_t s) {
+                          int num_pages, float scale, int window, int* status, cudaStream_t s, ScoreExtras ex = ScoreExtras{}) {
     static bool attr_set = false;
     if (!attr_set && PRE_SMEM_BYTES > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HPC, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              PRE_SMEM_BYTES);
         if (e != cudaSuccess) { imp_set_error("imp_attn_prefill: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
     }
     const int G = Hq / Hkv;
     dim3 grid(n_tiles, Hkv * ((G + HPC - 1) / HPC));
-    imp_launch(attn_prefill_kernel<HPC>, grid, dim3(2 * HPC * 32), (size_t)PRE_SMEM_BYTES, s, (__nv_bfloat16*)out, out_stride,
+    imp_launch(attn_prefill_kernel<HPC, BIAS>, grid, dim3(2 * HPC * 32), (size_t)PRE_SMEM_BYTES, s, (__nv_bfloat16*)out, out_stride,
                (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_stride,
                seq_of_token, positions, tile_tok0, tile_rows, n_seqs, Hq, Hkv, P, num_pages,
-               scale * 1.4426950408889634f, window, status);
+               scale * 1.4426950408889634f, window, status, ex);
     IMP_RETURN_LAUNCH();
 }
 
@@ -1599,6 +1686,28 @@ IMP_API int imp_attn_prefill(void* out, int64_t out_stride, const void* q, int64
     if (G == 1) return launch_prefill<1>(ARGS);
     if (G == 2) return launch_prefill<2>(ARGS);
     return launch_prefill<4>(ARGS);
+#undef ARGS
+}
+
+// The tiled prefill kernel with a score bias by distance and a sink (see ScoreExtras; either table may be null).
+IMP_API int imp_attn_prefill_bias(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kc,
+                                  const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                                  const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles,
+                                  int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale, int window,
+                                  const float* bias_l2, int n_dist, const float* sink_l2, int* status, void* stream) {
+    if (n_tiles == 0) return 0;
+    if (int rc = check_common(out, q, kc, vc, block_table, out_stride, q_stride, Hq, Hkv, P, num_pages)) return rc;
+    IMP_CHECK_ARG(seq_of_token && positions && tile_tok0 && tile_rows, "imp_attn_prefill_bias: null pointer");
+    IMP_CHECK_ARG(!bias_l2 || n_dist > 0, "imp_attn_prefill_bias: a bias table needs at least one distance");
+    const int G = Hq / Hkv;
+    IMP_CHECK_ARG((int64_t)Hkv * ((G + 3) / 4) <= 65535, "imp_attn_prefill_bias: too many head groups");
+    cudaStream_t s = (cudaStream_t)stream;
+    const ScoreExtras ex{bias_l2, n_dist, sink_l2};
+#define ARGS out, out_stride, q, q_stride, kc, vc, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows, \
+             n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale, window, status, s, ex
+    if (G == 1) return launch_prefill<1, true>(ARGS);
+    if (G == 2) return launch_prefill<2, true>(ARGS);
+    return launch_prefill<4, true>(ARGS);
 #undef ARGS
 }
 

@@ -1,0 +1,414 @@
+"""Kazedra against the plain implementation (tests/plain/kazedra_plain.py): each mixer alone through the
+part bench, whole models through the trace runner in every way of cutting, and greedy generation through
+the engine's own entry point.  Weights are made here so that a fault shows: distance biases and sinks
+several units large, decays spread over (0, 1), convolution taps of order one."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from imp_b200.cache.manager import PagedKVSpec, StateSpec
+from imp_b200.parts.bench import PartBench
+from imp_b200.parts.plan import PartSpec
+from plain import kazedra_plain as K
+from replay_helpers import collect, mixed, portions, round64, run_trace, tail_decode, whole
+from safetensors_io import save_safetensors
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+NAME = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+def close(got, want, dtype, what=""):
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = max(float(want.abs().max()), 1e-3)
+    atol, rtol = (3e-5 * scale, 3e-5) if dtype == torch.float32 else (0.025 * scale, 0.025)
+    err = (got - want).abs()
+    assert (err <= atol + rtol * want.abs()).all(), f"{what}: max error {err.max().item():.3g} (scale {scale:.3g})"
+
+
+def run_mixer(bench, part, x, ctx, cache):
+    torch.cuda.synchronize()
+    out = part.forward(x.to(DEV), ctx, cache)
+    bench.sync()
+    return out.clone()
+
+
+# ------------------------------------------------------------------ weights
+def left_weights(d, c, buckets, seed, strong=3.0):
+    H, G, D = c["heads"], c["kv_heads"], c["dim"]
+    s = 1.0 / math.sqrt(d)
+    return {"q": rnd(H * D, d, seed=seed, scale=s), "q.b": rnd(H * D, seed=seed + 1, scale=0.3),
+            "k": rnd(G * D, d, seed=seed + 2, scale=s), "k.b": rnd(G * D, seed=seed + 3, scale=0.3),
+            "q.norm": 1 + 0.2 * rnd(H * D, seed=seed + 4), "k.norm": 1 + 0.2 * rnd(G * D, seed=seed + 5),
+            "rel": rnd(buckets, H, seed=seed + 6, scale=strong), "sink": 1.0 + rnd(H, seed=seed + 7, scale=2.0),
+            "o": rnd(d, H * D, seed=seed + 8, scale=1.0 / math.sqrt(H * D)), "o.b": rnd(d, seed=seed + 9, scale=0.2)}
+
+
+def right_weights(d, c, seed):
+    H, G, D, Dv, taps = c["heads"], c["kv_heads"], c["dim"], c["vdim"], c["conv"]
+    s = 1.0 / math.sqrt(d)
+    return {"q": rnd(G * D, d, seed=seed, scale=2 * s), "q.conv": rnd(G * D, taps, seed=seed + 1, scale=0.7),
+            "k": rnd(G * D, d, seed=seed + 2, scale=2 * s), "k.conv": rnd(G * D, taps, seed=seed + 3, scale=0.7),
+            "v": rnd(H * Dv, d, seed=seed + 4, scale=2 * s), "v.conv": rnd(H * Dv, taps, seed=seed + 5, scale=0.7),
+            "b": rnd(H, d, seed=seed + 6, scale=2 * s), "A_log": rnd(H, seed=seed + 7, scale=1.0),
+            "norm": 1 + 0.2 * rnd(Dv, seed=seed + 8), "a": rnd(H, d, seed=seed + 9, scale=2 * s),
+            "dt_bias": rnd(H, seed=seed + 10, scale=1.0), "g": rnd(H * Dv, d, seed=seed + 11, scale=2 * s),
+            "o": rnd(d, H * Dv, seed=seed + 12, scale=1.0 / math.sqrt(H * Dv))}
+
+
+LEFT_NAMES = {"q": "q_proj", "q.b": "q_bias", "k": "k_proj", "k.b": "k_bias", "q.norm": "q_norm", "k.norm": "k_norm",
+              "rel": "rel_bias", "sink": "sink", "o": "o_proj", "o.b": "o_bias"}
+RIGHT_NAMES = {"q": "q_proj", "q.conv": "q_conv", "k": "k_proj", "k.conv": "k_conv", "v": "v_proj", "v.conv": "v_conv",
+               "b": "beta_proj", "A_log": "a_log", "norm": "out_norm", "a": "a_proj", "dt_bias": "dt_bias", "g": "gate_proj",
+               "o": "o_proj"}
+
+
+# ------------------------------------------------------- the attention mixer alone
+LEFT_CASES = [
+    # heads, kv heads, head size, width, buckets, largest distance, every, page size
+    dict(heads=6, kv_heads=3, dim=24, d=72, buckets=12, bias_max=40, every=5, page=4),
+    dict(heads=4, kv_heads=4, dim=40, d=48, buckets=7, bias_max=9, every=64, page=16),
+    dict(heads=5, kv_heads=1, dim=64, d=80, buckets=32, bias_max=300, every=1, page=8),
+]
+
+
+def left_setup(dtype, case, strong=3.0):
+    c = {"heads": case["heads"], "kv_heads": case["kv_heads"], "dim": case["dim"], "vdim": case["dim"], "bias_max": case["bias_max"],
+         "scale": 1.3 / math.sqrt(case["dim"]), "q_temp": {"coef": 0.4, "every": case["every"]}}
+    bench = PartBench(NAME[dtype], [PagedKVSpec(c["kv_heads"], c["dim"], 0)], page_size=case["page"], num_pages=256, max_tokens=512,
+                      max_seq_len=512)
+    w = {k: v.to(dtype) for k, v in left_weights(case["d"], c, case["buckets"], seed=100, strong=strong).items()}
+    params = {"hidden_size": case["d"], "num_heads": c["heads"], "num_kv_heads": c["kv_heads"], "head_dim": c["dim"], "scale": c["scale"],
+              "norm_eps": 2e-5, "q_temp_coef": 0.4, "q_temp_every": case["every"], "bias_max_distance": case["bias_max"]}
+    part = bench.build("mixer", PartSpec("sink_bias_attention", params), {LEFT_NAMES[k]: v.to(DEV) for k, v in w.items()})
+    return bench, part, c, {"m." + k: v.double() for k, v in w.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", LEFT_CASES)
+def test_sink_bias_attention_whole_portions_and_decoding(dtype, case):
+    """Prompts longer than the largest distance of the table, whole; then the same in portions down to one and two
+    tokens beside another sequence that decodes; every position against the plain function."""
+    bench, part, c, W = left_setup(dtype, case)
+    d = case["d"]
+    lengths = [93, 11]
+    xs = [rnd(n, d, seed=20 + i).to(dtype) for i, n in enumerate(lengths)]
+    want = [K.sink_bias_attention(x.double(), W, "m.", c, 2e-5) for x in xs]
+    ctx = bench.prepare([(f"w{i}", [1] * n, []) for i, n in enumerate(lengths)])
+    out = run_mixer(bench, part, torch.cat(xs), ctx, bench.cache_view(0))
+    bench.commit()
+    close(out[:93], want[0], dtype, "whole")
+    close(out[93:], want[1], dtype, "whole, second sequence")
+    done, outs, other = 0, [], 0
+    for n in (10, 2, 20, 1, 4, 2, 33, 1, 1, 1, 2, 16):
+        es, parts = [("p0", [1] * n, [])], [xs[0][done:done + n]]
+        if other < lengths[1]:
+            es.append(("p1", [1], []))
+            parts.append(xs[1][other:other + 1])
+        ctx = bench.prepare(es)
+        o = run_mixer(bench, part, torch.cat(parts), ctx, bench.cache_view(0))
+        bench.commit()
+        outs.append(o[:n])
+        if other < lengths[1]:
+            close(o[n:], want[1][other:other + 1], dtype, f"decoded token {other}")
+            other += 1
+        done += n
+    assert done == 93
+    close(torch.cat(outs), want[0], dtype, "portions")
+
+
+def test_sink_and_bias_show_in_the_output():
+    """The plain function without the sink, or with the table shifted by one distance, is far from the part's output:
+    the comparison above would not pass by accident."""
+    case = LEFT_CASES[0]
+    bench, part, c, W = left_setup(torch.float32, case)
+    x = rnd(60, case["d"], seed=7)
+    ctx = bench.prepare([("a", [1] * 60, [])])
+    out = run_mixer(bench, part, x, ctx, bench.cache_view(0)).cpu().double()
+    want = K.sink_bias_attention(x.double(), W, "m.", c, 2e-5)
+    assert (out - want).abs().max() < 1e-4 * want.abs().max()
+    no_sink = dict(W)
+    no_sink["m.sink"] = torch.full_like(W["m.sink"], -1e9)
+    assert (K.sink_bias_attention(x.double(), no_sink, "m.", c, 2e-5) - want).abs().max() > 0.05 * want.abs().max()
+    shifted = dict(W)
+    shifted["m.rel"] = torch.roll(W["m.rel"], 1, 0)
+    assert (K.sink_bias_attention(x.double(), shifted, "m.", c, 2e-5) - want).abs().max() > 0.05 * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_far_key_among_hundreds(dtype):
+    """Token 3 is given a key that every later query prefers by a wide margin, and the bias beyond the largest distance
+    is strongly positive: the output 400 tokens later is that token's value, in a prompt and decoded alone."""
+    case = dict(heads=2, kv_heads=1, dim=32, d=32, buckets=8, bias_max=20, every=64, page=16)
+    c = {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "bias_max": 20, "scale": 1.0, "q_temp": {"coef": 0.0, "every": 64}}
+    w = left_weights(32, c, 8, seed=300, strong=0.1)
+    w["q"] = torch.cat([torch.eye(32), torch.eye(32)]) * 1.0
+    w["k"] = torch.eye(32)
+    w["q.b"].zero_(), w["k.b"].zero_(), w["q.norm"].fill_(1.0), w["k.norm"].fill_(1.0)
+    w["sink"].fill_(-3.0)
+    w["rel"][-1] = 2.0
+    w = {k: v.to(dtype) for k, v in w.items()}
+    bench = PartBench(NAME[dtype], [PagedKVSpec(1, 32, 0)], page_size=16, num_pages=64, max_tokens=512, max_seq_len=512)
+    params = {"hidden_size": 32, "num_heads": 2, "num_kv_heads": 1, "head_dim": 32, "scale": 1.0, "norm_eps": 1e-6,
+              "q_temp_coef": 0.0, "q_temp_every": 64, "bias_max_distance": 20}
+    part = bench.build("mixer", PartSpec("sink_bias_attention", params), {LEFT_NAMES[k]: v.to(DEV) for k, v in w.items()})
+    T = 420
+    x = rnd(T, 32, seed=301, scale=0.05)
+    x[3] = 0
+    x[3, 5] = 6.0                         # the far key: a large component along dimension 5
+    x[400:, 5] += 3.0                     # queries that look along it
+    x = x.to(dtype)
+    W = {"m." + k: v.double() for k, v in w.items()}
+    want = K.sink_bias_attention(x.double(), W, "m.", c, 1e-6)
+    ctx = bench.prepare([("a", [1] * 410, [])])
+    out = run_mixer(bench, part, x[:410], ctx, bench.cache_view(0))
+    bench.commit()
+    close(out, want[:410], dtype, "prompt")
+    for t in range(410, T):
+        ctx = bench.prepare([("a", [1], [])])
+        o = run_mixer(bench, part, x[t:t + 1], ctx, bench.cache_view(0))
+        bench.commit()
+        close(o, want[t:t + 1], dtype, f"decoded {t}")
+    # the far token carries the output: leaving it out changes the result beyond any tolerance
+    x2 = x.clone()
+    x2[3] = 0
+    assert (K.sink_bias_attention(x2.double(), W, "m.", c, 1e-6)[405] - want[405]).abs().max() > 0.3 * want[405].abs().max()
+
+
+# ----------------------------------------------------- the recurrent mixer alone
+RIGHT_CASES = [
+    dict(heads=6, kv_heads=3, dim=20, vdim=12, conv=3, d=72),
+    dict(heads=2, kv_heads=2, dim=70, vdim=33, conv=5, d=40),
+    dict(heads=4, kv_heads=1, dim=128, vdim=64, conv=1, d=64),
+    dict(heads=1, kv_heads=1, dim=8, vdim=100, conv=2, d=24),
+]
+
+
+def right_setup(dtype, case, slots=4):
+    c = {k: case[k] for k in ("heads", "kv_heads", "dim", "vdim", "conv")}
+    C = 2 * c["kv_heads"] * c["dim"] + c["heads"] * c["vdim"]
+    spec = StateSpec(tensors=(("S", (c["heads"], c["dim"], c["vdim"]), "float32"), ("conv", (max(c["conv"] - 1, 1), C), "float32")))
+    bench = PartBench(NAME[dtype], [spec], slots=slots, max_tokens=512, max_seq_len=512)
+    w = {k: v.to(dtype) for k, v in right_weights(case["d"], c, seed=200).items()}
+    params = {"hidden_size": case["d"], "num_heads": c["heads"], "num_kv_heads": c["kv_heads"], "key_dim": c["dim"],
+              "value_dim": c["vdim"], "conv_taps": c["conv"], "norm_eps": 2e-5}
+    part = bench.build("mixer", PartSpec("gated_delta_rule", params), {RIGHT_NAMES[k]: v.to(DEV) for k, v in w.items()})
+    return bench, part, c, {"m." + k: v.double() for k, v in w.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", RIGHT_CASES)
+def test_gated_delta_rule_whole_portions_decoding_and_reused_slots(dtype, case):
+    bench, part, c, W = right_setup(dtype, case, slots=2)
+    d = case["d"]
+    lengths = [75, 9]
+    xs = [rnd(n, d, seed=40 + i).to(dtype) for i, n in enumerate(lengths)]
+    want = [K.gated_delta_rule(x.double(), W, "m.", c, 2e-5) for x in xs]
+    ctx = bench.prepare([(f"w{i}", [1] * n, []) for i, n in enumerate(lengths)])
+    out = run_mixer(bench, part, torch.cat(xs), ctx, bench.cache_view(0))
+    bench.commit()
+    close(out[:75], want[0], dtype, "whole")
+    close(out[75:], want[1], dtype, "whole, second sequence")
+    # both slots go back and are used again: the new requests must start from zero state
+    bench.end("w0")
+    bench.end("w1")
+    done, outs, other = 0, [], 0
+    for n in (10, 2, 1, 1, 20, 1, 4, 2, 2, 1, 17, 3, 1, 1, 1, 1, 1, 1, 2, 3):
+        es, parts = [("p0", [1] * n, [])], [xs[0][done:done + n]]
+        if other < lengths[1]:
+            es.append(("p1", [1], []))
+            parts.append(xs[1][other:other + 1])
+        ctx = bench.prepare(es)
+        o = run_mixer(bench, part, torch.cat(parts), ctx, bench.cache_view(0))
+        bench.commit()
+        outs.append(o[:n])
+        if other < lengths[1]:
+            close(o[n:], want[1][other:other + 1], dtype, f"decoded token {other}")
+            other += 1
+        done += n
+    assert done == 75
+    close(torch.cat(outs), want[0], dtype, "portions")
+
+
+def test_delta_rule_portions_change_no_bit():
+    """The recurrence walks tokens in order with sums whose order the sizes fix: a prompt in one piece and in
+    pieces gives the same bits in float32."""
+    case = RIGHT_CASES[0]
+    bench, part, c, W = right_setup(torch.float32, case)
+    x = rnd(50, case["d"], seed=77)
+    ctx = bench.prepare([("a", [1] * 50, [])])
+    whole_out = run_mixer(bench, part, x, ctx, bench.cache_view(0))
+    bench.commit()
+    outs, done = [], 0
+    for n in (3, 2, 1, 30, 1, 13):
+        ctx = bench.prepare([("b", [1] * n, [])])
+        outs.append(run_mixer(bench, part, x[done:done + n], ctx, bench.cache_view(0)))
+        bench.commit()
+        done += n
+    assert torch.equal(torch.cat(outs), whole_out)
+
+
+def test_long_decay_and_state_carry():
+    """300 tokens one by one: the state is the only memory; its decay and correction against the plain recurrence."""
+    case = RIGHT_CASES[1]
+    bench, part, c, W = right_setup(torch.float32, case)
+    x = rnd(300, case["d"], seed=78)
+    want = K.gated_delta_rule(x.double(), W, "m.", c, 2e-5)
+    for t in range(300):
+        ctx = bench.prepare([("a", [1], [])])
+        o = run_mixer(bench, part, x[t:t + 1], ctx, bench.cache_view(0))
+        bench.commit()
+        if t < 4 or t > 290 or t % 37 == 0:
+            close(o, want[t:t + 1], torch.float32, f"token {t}")
+
+
+# --------------------------------------------------------------- whole models
+def layer(left, right, ls, rs, ff):
+    return {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": ls, "right_scale": rs},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def L(heads, kv, dim, bias_max, every, coef=0.35, scale=None):
+    return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "bias_max": bias_max, "scale": scale or 1.2 / math.sqrt(dim),
+            "q_temp": {"coef": coef, "every": every}}
+
+
+def R(heads, kv, dim, vdim, conv):
+    return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+# K1: two layers that differ in every size; the second has no feed-forward; 8 and 6 rows in the distance tables.
+# K2: three layers, head sizes 64 / 16 / 48, one key head for many, five taps, a width that is no power of two.
+MODELS = {
+    "K1": ({"architecture": "Kazedra", "vocab": 97, "width": 64, "norm": {"eps": 3e-5}, "logit_scale": 1.7,
+            "layers": [layer(L(4, 2, 16, 20, 7), R(2, 1, 24, 40, 3), 0.6, 1.1, 72),
+                       layer(L(3, 3, 32, 11, 5), R(4, 4, 16, 16, 2), 1.2, 0.7, 0)]}, [8, 6], 4),
+    "K2": ({"architecture": "Kazedra", "vocab": 211, "width": 112, "norm": {"eps": 1e-6}, "logit_scale": 0.4,
+            "layers": [layer(L(4, 1, 64, 100, 32), R(4, 2, 32, 48, 5), 0.9, 0.8, 152),
+                       layer(L(2, 2, 16, 24, 3), R(2, 2, 64, 24, 4), 0.5, 1.3, 96),
+                       layer(L(6, 2, 48, 64, 64), R(3, 1, 40, 56, 1), 1.0, 1.0, 0)]}, [16, 10, 32], 16),
+}
+LENGTHS = {"K1": (1, 23, 75, 40, 130, 64), "K2": (150, 2, 33, 201, 64, 97)}
+
+
+def make_weights(cfg, buckets, seed):
+    d = cfg["width"]
+    W = {"embed": rnd(cfg["vocab"], d, seed=seed), "final.norm": 0.2 * rnd(d, seed=seed + 1),
+         "head": rnd(cfg["vocab"], d, seed=seed + 2, scale=1.0 / math.sqrt(d))}
+    for i, lay in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        W[p + "norm1"] = 0.2 * rnd(d, seed=seed + 10 * i + 3)
+        for k, v in left_weights(d, lay["mixer"]["left"], buckets[i], seed + 1000 * (i + 1)).items():
+            W[p + "mix.left." + k] = v
+        for k, v in right_weights(d, lay["mixer"]["right"], seed + 1000 * (i + 1) + 500).items():
+            W[p + "mix.right." + k] = v
+        if lay["mlp"]:
+            ff = lay["mlp"]["ff"]
+            W[p + "norm2"] = 0.2 * rnd(d, seed=seed + 10 * i + 4)
+            W[p + "mlp.gate"] = rnd(ff, d, seed=seed + 10 * i + 5, scale=1.0 / math.sqrt(d))
+            W[p + "mlp.up"] = rnd(ff, d, seed=seed + 10 * i + 6, scale=1.0 / math.sqrt(d))
+            W[p + "mlp.down"] = rnd(d, ff, seed=seed + 10 * i + 7, scale=1.0 / math.sqrt(ff))
+    return {k: v.to(torch.bfloat16) for k, v in W.items()}
+
+
+@pytest.fixture(scope="module")
+def kazedra_folders(tmp_path_factory):
+    out = {}
+    for n, (name, (cfg, buckets, page)) in enumerate(MODELS.items()):
+        folder = str(tmp_path_factory.mktemp(f"kazedra_{name}"))
+        W = make_weights(cfg, buckets, seed=50 + n)
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        save_safetensors(os.path.join(folder, "model.safetensors"), W)
+        g = torch.Generator().manual_seed(n)
+        reqs = {f"r{i}": torch.randint(0, cfg["vocab"], (m,), generator=g).tolist() for i, m in enumerate(LENGTHS[name])}
+        ref = {rid: K.forward(cfg, W, ids).float().numpy() for rid, ids in reqs.items()}
+        out[name] = (folder, cfg, page, W, reqs, ref)
+    return out
+
+
+def check_rows(rows, reqs, ref, dtype):
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    atol, rtol = (1e-4 * max(scale, 1.0), 1e-4) if dtype == "float32" else (0.03 * scale, 0.03)
+    n = 0
+    for rid, ids in reqs.items():
+        for p in range(len(ids)):
+            got, want = rows[(rid, p)], ref[rid][p]
+            bad = np.abs(got - want) > atol + rtol * np.abs(want)
+            assert not bad.any(), f"request {rid} position {p}: max error {np.abs(got - want).max():.3g} (allowed {atol:.3g}) in {dtype}"
+            n += 1
+    assert n == sum(len(v) for v in reqs.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["K1", "K2"])
+def test_replay_all_ways_of_cutting(name, dtype, kazedra_folders, tmp_path):
+    folder, cfg, page, W, reqs, ref = kazedra_folders[name]
+    V = cfg["vocab"]
+    longest = round64(max(len(v) for v in reqs.values()))
+    results = {}
+    cuts = [("whole", whole(reqs), longest), ("tail", tail_decode(reqs), longest), ("portions", portions(reqs), longest),
+            ("wide_portions", portions(reqs, sizes=(70, 2, 33, 64, 1, 100)), longest)]
+    for label, steps, pool in cuts:
+        out = run_trace(folder, dtype, steps, pool, str(tmp_path / label), V, page_size=page)
+        rows = collect(steps, out)
+        check_rows(rows, reqs, ref, dtype)
+        results[label] = rows
+    steps, peak = mixed(reqs)
+    assert max(len(s["entries"]) for s in steps) == 4
+    assert peak < sum(round64(len(v)) for v in reqs.values()), "the pool must be too small to avoid reuse"
+    out = run_trace(folder, dtype, steps, peak, str(tmp_path / "mixed"), V, page_size=page)
+    rows = collect(steps, out)
+    check_rows(rows, reqs, ref, dtype)
+    results["mixed"] = rows
+    if dtype == "float32":
+        # every reduction of the float32 path has an order that depends on the row alone
+        for label in [c[0] for c in cuts[1:]] + ["mixed"]:
+            for key, row in results["whole"].items():
+                assert np.array_equal(row, results[label][key]), f"{label}: {key} differs from the whole run"
+
+
+def test_greedy_generation_through_the_engine(kazedra_folders):
+    """Prompts of unequal length through submit / schedule / step / sample with short prefill portions; the tokens
+    are those of the plain model's argmax, and pages and slots all come back."""
+    from imp_b200 import Engine, EngineConfig, GenerateParams
+    folder, cfg, page, W, reqs, ref = kazedra_folders["K1"]
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (1, 7, 30, 12, 3)]
+
+    def plain_generate(ids, n):
+        ids, out = list(ids), []
+        for _ in range(n):
+            tok = int(torch.argmax(K.forward(cfg, W, ids)[-1]))
+            out.append(tok)
+            ids.append(tok)
+        return out
+
+    want = [plain_generate(p, 8) for p in prompts]
+    eng = Engine.from_folder(folder, EngineConfig(compute_dtype="float32", kv_block_size=page, max_batch_size=3, max_seq_len=256,
+                                                  kv_cache_tokens=1024, max_batch_tokens=32, prefill_chunk_size=8))
+    got = eng.generate(prompts, GenerateParams(max_tokens=8, temperature=0.0))
+    assert got == want
+    assert eng.free_pages() == eng.num_pages and not eng.has_work()
+    info = eng.info()
+    assert info["cache"]["free_slots"] == info["cache"]["slots"]
+    # the same with CUDA graphs for the decode steps in bfloat16: first tokens from well separated logits agree
+    eng16 = Engine.from_folder(folder, EngineConfig(compute_dtype="bfloat16", kv_block_size=page, max_batch_size=4, max_seq_len=256,
+                                                    kv_cache_tokens=1024, max_batch_tokens=64))
+    got16 = eng16.generate(prompts, GenerateParams(max_tokens=8, temperature=0.0))
+    for p, g16, w in zip(prompts, got16, want):
+        lg = K.forward(cfg, W, p)[-1]
+        top2 = torch.topk(lg, 2).values
+        if float(top2[0] - top2[1]) > 0.1 * float(lg.abs().max()):
+            assert g16[0] == w[0]
