@@ -722,8 +722,26 @@ def run_arch(args):
     and in 512-token portions, and decode steps of `--batch` sequences at context 2,048, device time between CUDA events."""
     peaks, peak_src = read_peaks()
     layers, vocab, B = args.layers or 4, 32768, args.batch
+    if args.only in ("prefill", "decode"):
+        # one phase of one shape alone (for profilers): --tokens / --chunk / --context as for the default model
+        width, heads, kv, ff = ARCH_SHAPES[args.shape]
+        rng = random.Random(0)
+        eng, _ = make_engine(kazedra_config(width, heads, kv, ff, layers, vocab), args, B, 4096)
+        if args.only == "prefill":
+            ms = time_prefill(eng, rng, vocab, args.tokens or 2048, args.chunk, reps=max(1, args.steps))
+            print(json.dumps({"arch": "kazedra", "only": "prefill", "shape": args.shape, "layers": layers, "tokens": args.tokens or 2048,
+                              "chunk": args.chunk, "ms": spread(ms)}))
+        else:
+            reqs = start_decoding(eng, rng, vocab, B, args.context or 2048, args.steps + args.warmup + 16)
+            for _ in range(args.warmup):
+                eng.step()
+            ms = timed_steps(eng, args.steps, B) / args.steps
+            print(json.dumps({"arch": "kazedra", "only": "decode", "shape": args.shape, "layers": layers, "batch": B,
+                              "context": args.context or 2048, "ms_per_step": round(ms, 4)}))
+            stop(eng, reqs)
+        return 0
     out = {"arch": "kazedra", "beside": "qwen3", "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
-    with Clocks() as clocks:
+    with ClockSampler() as clocks:
         for name, (width, heads, kv, ff) in ARCH_SHAPES.items():
             models = {"kazedra": kazedra_config(width, heads, kv, ff, layers, vocab),
                       "qwen3": dict(MODEL, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
@@ -790,6 +808,7 @@ def main():
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
     ap.add_argument("--arch", default="", choices=["", "kazedra"],
                     help="prefill and decode of this architecture beside the Qwen3 decoder at equal sizes (not the default workload)")
+    ap.add_argument("--shape", default="8b", choices=["1b", "8b"], help="with --arch and --only: which of the shapes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
     ap.add_argument("--quick", action="store_true", help="skip the 2,048-step protocol runs and the yardsticks")
     ap.add_argument("--context", type=int, default=0,
@@ -806,6 +825,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.arch:
+        return run_arch(args)
     if args.only == "timeline":
         return run_timeline(args)
     if args.only == "mixed":

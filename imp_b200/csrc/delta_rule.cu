@@ -7,11 +7,12 @@
 // state) followed by silu; q and k are then unit vectors per head and q carries D^(-1/2).
 //
 // Four kernels, all 32-bit arithmetic on 32-bit state whatever the activation type:
-//   gdr_prepare     one CTA per token: convolution + silu of every channel, unit q and k, beta and decay
+//   gdr_prepare     one CTA per token and head: convolution + silu of its channels, unit q and k; beta and decay
 //   gdr_conv_state  the last taps - 1 inputs of every sequence of the batch go to its state slot
 //   gdr_scan        the recurrence; a CTA owns 32 value columns of one head of one sequence and walks
 //                   the sequence's new tokens in order; four lanes share a column, each holding a
-//                   quarter of it in registers, so no state travels between tokens but through registers
+//                   quarter of it in registers, so no state travels between tokens but through registers;
+//                   the tokens' inputs arrive through a two-deep cp.async ring
 //   gdr_output      per head: o / rms(o) * w * silu(gate)
 // Every column of S evolves independently of the others, which is what the scan kernel's split rests on.
 // A token's result depends on the tokens before it only through S and the convolution's inputs, and the
@@ -25,7 +26,11 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // proj: [T, ld] activations, columns [q: G*D | k: G*D | v: H*Dv | gate: H*Dv | b: H | a: H].
 // conv_w: [C, taps] float32 with C = 2*G*D + H*Dv (the last tap is the current token's).
 // conv_state: [slots, taps - 1, C] float32: the inputs of the taps - 1 tokens before the portion.
-constexpr int GP_BLOCK = 256;
+// grid (2G + H + 1, T): a CTA makes one head of one token (a q head, a k head or a v head: convolution, silu, and
+// for q and k the unit norm), the last CTA of a token its H step sizes and decays.  So a decode step of a few
+// tokens still spreads over the device.
+constexpr int GP_BLOCK = 128;
+constexpr int GP_MAX_D = 256;
 
 template <typename TA>
 __global__ void __launch_bounds__(GP_BLOCK) gdr_prepare_kernel(
@@ -35,44 +40,55 @@ __global__ void __launch_bounds__(GP_BLOCK) gdr_prepare_kernel(
     float* __restrict__ kn, float* __restrict__ vc, float* __restrict__ beta, float* __restrict__ decay, int* status) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float ch[];   // [C] channels after convolution and silu
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float scratch[33];
+    const int unit = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
     const int nqk = G * D, C = 2 * nqk + H * Dv;
     const int seq = seq_of_token[t];
     if (seq < 0 || seq >= n_seqs) {
-        if (tid == 0) imp_report(status, IMP_BAD_SEQUENCE);
+        if (tid == 0 && unit == 0) imp_report(status, IMP_BAD_SEQUENCE);
+        return;
+    }
+    if (unit == 2 * G + H) {
+        for (int hh = tid; hh < H; hh += GP_BLOCK) {
+            const TA* row = proj + (int64_t)t * ld + C + H * Dv;
+            const float b = to_float(row[hh]), a = to_float(row[H + hh]);
+            beta[(int64_t)t * H + hh] = 1.f / (1.f + expf(-b));
+            decay[(int64_t)t * H + hh] = expf(-expf(a_log[hh]) * softplus_f(a + dt_bias[hh]));
+        }
         return;
     }
     const int start = q_start[seq];
     const int n = t - start;                 // index of the token inside its portion
     const float* st = conv_state + (int64_t)slots[seq] * (taps - 1) * C;
-    for (int c = tid; c < C; c += GP_BLOCK) {
+    auto channel = [&](int c) {
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
             const int idx = n - (taps - 1) + j;
             const float x = idx >= 0 ? to_float(proj[(int64_t)(start + idx) * ld + c]) : st[(int64_t)(taps - 1 + idx) * C + c];
             acc = fmaf(conv_w[(int64_t)c * taps + j], x, acc);
         }
-        ch[c] = silu_f(acc);
+        return silu_f(acc);
+    };
+    if (unit >= 2 * G) {                     // a value head: no norm
+        const int hh = unit - 2 * G;
+        for (int d = tid; d < Dv; d += GP_BLOCK) vc[(int64_t)t * H * Dv + hh * Dv + d] = channel(2 * nqk + hh * Dv + d);
+        return;
     }
-    __syncthreads();
-    // unit q and k per head: a warp per head
-    const float q_scale = rsqrtf((float)D);
-    for (int hh = warp; hh < 2 * G; hh += GP_BLOCK / 32) {
-        const float* x = ch + hh * D;
-        float ss = 0.f;
-        for (int d = lane; d < D; d += 32) ss = fmaf(x[d], x[d], ss);
-        ss = warp_sum(ss);
-        const float r = rsqrtf(ss + 1e-6f) * (hh < G ? q_scale : 1.f);
-        float* dst = (hh < G ? qn + (int64_t)t * nqk + hh * D : kn + (int64_t)t * nqk + (hh - G) * D);
-        for (int d = lane; d < D; d += 32) dst[d] = x[d] * r;
+    // a q or k head: at most two channels a thread, unit norm over the head
+    float x[GP_MAX_D / GP_BLOCK], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < GP_MAX_D / GP_BLOCK; ++i) {
+        const int d = tid + i * GP_BLOCK;
+        x[i] = d < D ? channel(unit * D + d) : 0.f;
+        ss = fmaf(x[i], x[i], ss);
     }
-    for (int c = tid; c < H * Dv; c += GP_BLOCK) vc[(int64_t)t * H * Dv + c] = ch[2 * nqk + c];
-    if (tid < H) {
-        const TA* row = proj + (int64_t)t * ld + C + H * Dv;
-        const float b = to_float(row[tid]), a = to_float(row[H + tid]);
-        beta[(int64_t)t * H + tid] = 1.f / (1.f + expf(-b));
-        decay[(int64_t)t * H + tid] = expf(-expf(a_log[tid]) * softplus_f(a + dt_bias[tid]));
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss + 1e-6f) * (unit < G ? rsqrtf((float)D) : 1.f);
+    float* dst = unit < G ? qn + (int64_t)t * nqk + unit * D : kn + (int64_t)t * nqk + (unit - G) * D;
+#pragma unroll
+    for (int i = 0; i < GP_MAX_D / GP_BLOCK; ++i) {
+        const int d = tid + i * GP_BLOCK;
+        if (d < D) dst[d] = x[i] * r;
     }
 }
 
@@ -98,10 +114,25 @@ __global__ void gdr_conv_state_kernel(const TA* __restrict__ proj, int64_t ld, f
 constexpr int GS_COLS = 32;          // value columns per CTA
 constexpr int GS_LANES = 4;          // lanes that share a column
 constexpr int GS_BLOCK = GS_COLS * GS_LANES;
-constexpr int GS_CHUNK = 8;          // tokens whose q and k are staged together
 
-// DPL: key dimensions per lane (D <= 4 * DPL).  Lane r of a column holds dimensions [r * DPL, (r + 1) * DPL).
-template <int DPL>
+__device__ __forceinline__ void gs_cp_async16(void* dst, const void* src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void gs_cp_async4(void* dst, const void* src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(valid ? 4 : 0) : "memory");
+}
+
+// DPL: key dimensions per lane (D <= 4 * DPL).  Lane r of a column holds dimensions [r * DPL, (r + 1) * DPL) of its
+// column of S in registers.  The new tokens' q, k, v, decay and beta travel through a two-deep ring of chunks in shared
+// memory (cp.async; the next chunk is on its way while this one is computed); outputs leave a chunk at a time.
+//
+// Per token, with a = S^T k, c = S^T q (both on the state before the token) and kq = k . q:
+//     u = beta (v - g a);   o = g c + u kq;   S <- g S + k u^T
+// which is the recurrence's read-out S_new^T q written so that both reductions over the key dimension start from
+// the old state at once: one round of shuffles per token on the critical path instead of two.
+template <int DPL, bool VEC>
 __global__ void __launch_bounds__(GS_BLOCK) gdr_scan_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc, const float* __restrict__ beta,
     const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out, const int* __restrict__ q_start,
@@ -109,11 +140,14 @@ __global__ void __launch_bounds__(GS_BLOCK) gdr_scan_kernel(
     pdl_wait();
     pdl_launch_dependents();
     constexpr int ROW = DPL + 4;                          // padded so that the four lanes' 16-byte reads miss each other's banks
-    __shared__ __align__(16) float k_s[GS_CHUNK][GS_LANES * ROW];
-    __shared__ __align__(16) float q_s[GS_CHUNK][GS_LANES * ROW];
-    __shared__ float g_s[GS_CHUNK], b_s[GS_CHUNK];
-    const int tid = threadIdx.x, r = tid & (GS_LANES - 1);
-    const int col = blockIdx.x * GS_COLS + (tid >> 2);
+    constexpr int CH = DPL <= 32 ? 16 : 8;                // tokens per chunk
+    __shared__ __align__(16) float k_s[2][CH][GS_LANES * ROW];
+    __shared__ __align__(16) float q_s[2][CH][GS_LANES * ROW];
+    __shared__ float v_s[2][CH][GS_COLS];
+    __shared__ float g_s[2][CH], b_s[2][CH];
+    __shared__ float o_s[CH][GS_COLS];
+    const int tid = threadIdx.x, r = tid & (GS_LANES - 1), ci = tid >> 2;
+    const int col0 = blockIdx.x * GS_COLS, col = col0 + ci;
     const int h = blockIdx.y, seq = blockIdx.z;
     const int hk = h / (H / G);
     const int start = q_start[seq], n = q_start[seq + 1] - start;
@@ -127,57 +161,89 @@ __global__ void __launch_bounds__(GS_BLOCK) gdr_scan_kernel(
         s[i] = (live && d < D) ? S[(int64_t)d * Dv] : 0.f;
     }
     const int nqk = G * D;
-    for (int t0 = 0; t0 < n; t0 += GS_CHUNK) {
-        const int nt = min(GS_CHUNK, n - t0);
-        __syncthreads();
-        for (int e = tid; e < nt * GS_LANES * DPL; e += GS_BLOCK) {
-            const int tt = e / (GS_LANES * DPL), d = e - tt * (GS_LANES * DPL);
-            const int64_t src = (int64_t)(start + t0 + tt) * nqk + hk * D + d;
-            const int dst = (d / DPL) * ROW + d % DPL;
-            k_s[tt][dst] = d < D ? kn[src] : 0.f;
-            q_s[tt][dst] = d < D ? qn[src] : 0.f;
+    const int64_t hv = (int64_t)H * Dv;
+    auto load_chunk = [&](int t0, int buf) {
+        const int nt = min(CH, n - t0);
+        if (VEC) {
+            for (int e = tid; e < CH * DPL; e += GS_BLOCK) {          // 16 bytes = 4 dimensions, all inside one lane's run
+                const int tt = e / DPL, d = (e - tt * DPL) * 4;
+                const bool ok = tt < nt && d < D;
+                const int64_t src = ok ? (int64_t)(start + t0 + tt) * nqk + hk * D + d : 0;
+                const int dst = (d / DPL) * ROW + d % DPL;
+                gs_cp_async16(&k_s[buf][tt][dst], kn + src, ok);
+                gs_cp_async16(&q_s[buf][tt][dst], qn + src, ok);
+            }
+        } else {
+            for (int e = tid; e < CH * GS_LANES * DPL; e += GS_BLOCK) {
+                const int tt = e / (GS_LANES * DPL), d = e - tt * (GS_LANES * DPL);
+                const bool ok = tt < nt && d < D;
+                const int64_t src = ok ? (int64_t)(start + t0 + tt) * nqk + hk * D + d : 0;
+                const int dst = (d / DPL) * ROW + d % DPL;
+                gs_cp_async4(&k_s[buf][tt][dst], kn + src, ok);
+                gs_cp_async4(&q_s[buf][tt][dst], qn + src, ok);
+            }
         }
-        if (tid < nt) {
-            g_s[tid] = decay[(int64_t)(start + t0 + tid) * H + h];
-            b_s[tid] = beta[(int64_t)(start + t0 + tid) * H + h];
+        for (int e = tid; e < CH * GS_COLS; e += GS_BLOCK) {
+            const int tt = e / GS_COLS, c = e - tt * GS_COLS;
+            const bool ok = tt < nt && col0 + c < Dv;
+            gs_cp_async4(&v_s[buf][tt][c], vc + (ok ? (int64_t)(start + t0 + tt) * hv + (int64_t)h * Dv + col0 + c : 0), ok);
+        }
+        if (tid < CH) {
+            const bool ok = tid < nt;
+            const int64_t src = ok ? (int64_t)(start + t0 + tid) * H + h : 0;
+            gs_cp_async4(&g_s[buf][tid], decay + src, ok);
+            gs_cp_async4(&b_s[buf][tid], beta + src, ok);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    load_chunk(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < n; t0 += CH, buf ^= 1) {
+        const int nt = min(CH, n - t0);
+        if (t0 + CH < n) {
+            load_chunk(t0 + CH, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const int64_t tok = start + t0 + tt;
-            const float g = g_s[tt], b = b_s[tt];
-            const float v = live ? vc[tok * H * Dv + (int64_t)h * Dv + col] : 0.f;
-            const float4* k4 = reinterpret_cast<const float4*>(&k_s[tt][r * ROW]);
-            const float4* q4 = reinterpret_cast<const float4*>(&q_s[tt][r * ROW]);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPL / 4; ++i) {
-                const float4 kk = k4[i];
-                a0 = fmaf(s[4 * i], kk.x, a0);
-                a1 = fmaf(s[4 * i + 1], kk.y, a1);
-                a2 = fmaf(s[4 * i + 2], kk.z, a2);
-                a3 = fmaf(s[4 * i + 3], kk.w, a3);
-            }
-            float ks = (a0 + a1) + (a2 + a3);
-            ks += __shfl_xor_sync(0xffffffffu, ks, 1);
-            ks += __shfl_xor_sync(0xffffffffu, ks, 2);
-            const float u = b * (v - g * ks);             // S^T k after the decay is g times S^T k before it
-            a0 = a1 = a2 = a3 = 0.f;
+            const float g = g_s[buf][tt], b = b_s[buf][tt], v = v_s[buf][tt][ci];
+            const float4* k4 = reinterpret_cast<const float4*>(&k_s[buf][tt][r * ROW]);
+            const float4* q4 = reinterpret_cast<const float4*>(&q_s[buf][tt][r * ROW]);
+            float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f, e0 = 0.f, e1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPL / 4; ++i) {
                 const float4 kk = k4[i], qq = q4[i];
+                a0 = fmaf(s[4 * i], kk.x, a0);     a1 = fmaf(s[4 * i + 1], kk.y, a1);
+                a0 = fmaf(s[4 * i + 2], kk.z, a0); a1 = fmaf(s[4 * i + 3], kk.w, a1);
+                c0 = fmaf(s[4 * i], qq.x, c0);     c1 = fmaf(s[4 * i + 1], qq.y, c1);
+                c0 = fmaf(s[4 * i + 2], qq.z, c0); c1 = fmaf(s[4 * i + 3], qq.w, c1);
+                e0 = fmaf(kk.x, qq.x, e0);         e1 = fmaf(kk.y, qq.y, e1);
+                e0 = fmaf(kk.z, qq.z, e0);         e1 = fmaf(kk.w, qq.w, e1);
+            }
+            float a = a0 + a1, c = c0 + c1, kq = e0 + e1;
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            c += __shfl_xor_sync(0xffffffffu, c, 1);
+            kq += __shfl_xor_sync(0xffffffffu, kq, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            c += __shfl_xor_sync(0xffffffffu, c, 2);
+            kq += __shfl_xor_sync(0xffffffffu, kq, 2);
+            const float u = b * (v - g * a);
+#pragma unroll
+            for (int i = 0; i < DPL / 4; ++i) {
+                const float4 kk = k4[i];
                 s[4 * i] = fmaf(kk.x, u, g * s[4 * i]);
                 s[4 * i + 1] = fmaf(kk.y, u, g * s[4 * i + 1]);
                 s[4 * i + 2] = fmaf(kk.z, u, g * s[4 * i + 2]);
                 s[4 * i + 3] = fmaf(kk.w, u, g * s[4 * i + 3]);
-                a0 = fmaf(s[4 * i], qq.x, a0);
-                a1 = fmaf(s[4 * i + 1], qq.y, a1);
-                a2 = fmaf(s[4 * i + 2], qq.z, a2);
-                a3 = fmaf(s[4 * i + 3], qq.w, a3);
             }
-            float o = (a0 + a1) + (a2 + a3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (live && r == 0) out[tok * H * Dv + (int64_t)h * Dv + col] = o;
+            if (r == 0) o_s[tt][ci] = fmaf(u, kq, g * c);
+        }
+        __syncthreads();
+        for (int e = tid; e < nt * GS_COLS; e += GS_BLOCK) {
+            const int tt = e / GS_COLS, c = e - tt * GS_COLS;
+            if (col0 + c < Dv) out[(int64_t)(start + t0 + tt) * hv + (int64_t)h * Dv + col0 + c] = o_s[tt][c];
         }
     }
 #pragma unroll
@@ -217,31 +283,18 @@ IMP_API int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, i
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(proj && conv_w && conv_state && seq_of_token && q_start && slots && a_log && dt_bias && qn && kn && vc && beta && decay,
                   "imp_gdr_prepare: null pointer");
-    IMP_CHECK_ARG(G > 0 && H > 0 && H % G == 0 && D > 0 && Dv > 0 && taps >= 1 && H <= GP_BLOCK,
-                  "imp_gdr_prepare: bad sizes (heads %d over %d key heads, at most %d heads)", H, G, GP_BLOCK);
+    IMP_CHECK_ARG(G > 0 && H > 0 && H % G == 0 && D > 0 && D <= GP_MAX_D && Dv > 0 && taps >= 1 && n_tokens <= 65535,
+                  "imp_gdr_prepare: bad sizes (heads %d over %d key heads, key size %d of at most %d)", H, G, D, GP_MAX_D);
     const int C = 2 * G * D + H * Dv;
     IMP_CHECK_ARG(ld >= (int64_t)C + H * Dv + 2 * H, "imp_gdr_prepare: the projection's rows are too short");
-    const size_t smem = (size_t)C * 4;
-    IMP_CHECK_ARG(smem <= 200 * 1024, "imp_gdr_prepare: %d convolution channels do not fit shared memory", C);
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e = cudaSuccess;
-    if (act_dtype == IMP_F32) {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(gdr_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess)
-            imp_launch(gdr_prepare_kernel<float>, dim3(n_tokens), dim3(GP_BLOCK), smem, s, (const float*)proj, ld, conv_w, taps, conv_state,
-                       seq_of_token, q_start, slots, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, status);
-    } else {
-        if (smem > 48 * 1024)
-            e = cudaFuncSetAttribute(gdr_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess)
-            imp_launch(gdr_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(GP_BLOCK), smem, s, (const __nv_bfloat16*)proj, ld, conv_w,
-                       taps, conv_state, seq_of_token, q_start, slots, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay,
-                       status);
-    }
-    if (e != cudaSuccess) {
-        imp_set_error("imp_gdr_prepare: %s", cudaGetErrorString(e));
-        return (int)e;
-    }
+    const dim3 grid(2 * G + H + 1, n_tokens);
+    if (act_dtype == IMP_F32)
+        imp_launch(gdr_prepare_kernel<float>, grid, dim3(GP_BLOCK), 0, s, (const float*)proj, ld, conv_w, taps, conv_state, seq_of_token,
+                   q_start, slots, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, status);
+    else
+        imp_launch(gdr_prepare_kernel<__nv_bfloat16>, grid, dim3(GP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, conv_w, taps, conv_state,
+                   seq_of_token, q_start, slots, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, status);
     IMP_RETURN_LAUNCH();
 }
 
@@ -271,8 +324,13 @@ IMP_API int imp_gdr_scan(const float* qn, const float* kn, const float* vc, cons
     }
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid((Dv + GS_COLS - 1) / GS_COLS, H, n_seqs);
-#define GDR_SCAN(DPL) \
-    imp_launch(gdr_scan_kernel<DPL>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv)
+    // 16-byte copies of q and k rows need rows that start on 16 bytes: D a multiple of 4 and aligned buffers
+    const bool vec = D % 4 == 0 && (uintptr_t)qn % 16 == 0 && (uintptr_t)kn % 16 == 0;
+#define GDR_SCAN(DPL)                                                                                                                  \
+    do {                                                                                                                               \
+        if (vec) imp_launch(gdr_scan_kernel<DPL, true>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv); \
+        else imp_launch(gdr_scan_kernel<DPL, false>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv);    \
+    } while (0)
     if (D <= 16) GDR_SCAN(4);
     else if (D <= 32) GDR_SCAN(8);
     else if (D <= 64) GDR_SCAN(16);

@@ -48,8 +48,13 @@ struct MmaVariant {
     DecodeFusedFn decode_fused = nullptr;
     PrefillFn prefill = nullptr;
 };
+using PrefillTcBiasFn = int (*)(void*, int64_t, const void*, int64_t, int, const void*, const void*, const int*, int, const int*,
+                                const int*, const int*, const int*, int, int, int, int, int, int, float, int, const float*, int,
+                                const float*, int*, void*);
 struct TcVariant {
     void* handle = nullptr;
+    PrefillTcBiasFn prefill_bias = nullptr;
+    int (*bias_pad)() = nullptr;
     const char* (*last_error)() = nullptr;
     int (*supported)(int64_t, int64_t, int) = nullptr;
     PrefillTcFn prefill = nullptr;
@@ -143,6 +148,8 @@ TcVariant& tc_variant(int head_dim) {
     bind(v.handle, "imp_last_error", v.last_error, path);
     bind(v.handle, "imp_attn_prefill_tc_supported", v.supported, path);
     bind(v.handle, "imp_attn_prefill_tc", v.prefill, path);
+    bind(v.handle, "imp_attn_prefill_tc_bias", v.prefill_bias, path);
+    bind(v.handle, "imp_attn_prefill_tc_bias_pad", v.bias_pad, path);
     return g_tc[head_dim] = v;
 }
 
@@ -297,6 +304,8 @@ static bool prefill_tc_supported(const Tensor& q, const Tensor& out, const Atten
 // the pages directly for the sequences that bring one token (a decode step, or the leading rows of a mixed step), the
 // 32-token tiles for the rest.  False, with nothing done, where those kernels do not apply (float32, head sizes that are
 // no multiple of 16, rows that do not start on 16 bytes, no tables in the log2 domain, IMP_B200_ATTN_BIAS=generic).
+static bool prefill_tc_supported(const Tensor& q, const Tensor& out, const AttentionGeometry& g, const ImpCacheView& c);
+
 static bool bias_attention_mma(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
                                const std::vector<int>& tiling_ids, const AttentionExtras& ex) {
     Runtime& rt = *st.rt;
@@ -332,7 +341,21 @@ static bool bias_attention_mma(Step& st, Tensor out, const Tensor& q, const Atte
     for (int i = n_single; singles && i < st.B(); ++i)
         if (st.q_lens[(size_t)i] == 1) singles = false;
     if (singles) decode(first_rows(out, n_single), first_rows(q, n_single));
-    const Tiles& tiles = st.tiles.at((size_t)tiling_ids[singles ? 3 : 0]);
+    // portions of 64 tokens and more on the tensor-memory kernel in tiles of 128, where it takes the geometry and the
+    // caller has the table in that kernel's padded layout
+    const Tiles& wide = st.tiles.at((size_t)tiling_ids[1]);
+    const bool tc = wide.count && (!ex.bias || ex.bias_pad_l2) && prefill_tc_supported(q, out, g, c) &&
+                    tc_variant(g.dh).bias_pad() == ex.pad;
+    if (tc) {
+        TcVariant& tlib = tc_variant(g.dh);
+        check_variant(rt,
+                      tlib.prefill_bias(out.data, out.stride0, q.data, q.stride0, (int)rows(q), c.k_pages, c.v_pages, c.block_table,
+                                        c.bt_stride, st.view.seq_of_token, st.view.positions, wide.tok0, wide.rows, wide.count, st.B(),
+                                        g.hq, g.hkv, c.page_size, c.num_pages, g.scale, g.window, ex.bias_pad_l2, ex.n_dist, ex.sink_l2,
+                                        rt.status, rt.stream),
+                      "attention prefill (tcgen05, bias, sink)", tlib.last_error);
+    }
+    const Tiles& tiles = st.tiles.at((size_t)tiling_ids[tc ? (singles ? 4 : 2) : (singles ? 3 : 0)]);
     if (tiles.count)
         check_variant(rt,
                       lib.prefill_bias(out.data, out.stride0, q.data, q.stride0, c.k_pages, c.v_pages, c.block_table, c.bt_stride,

@@ -69,7 +69,12 @@ struct AttentionExtras {
     // the same tables times log2(e), for the kernels that exponentiate with base 2 (null: only the plain kernel runs)
     const float* bias_l2 = nullptr;
     const float* sink_l2 = nullptr;
+    // bias_l2 with `pad` entries in front of every head's row (zeros) and behind it (copies of the last entry):
+    // [hq, pad + n_dist + pad], what the tensor-memory prefill kernel reads without clamping
+    const float* bias_pad_l2 = nullptr;
+    int pad = 0;
 };
+constexpr int ATTENTION_BIAS_PAD = 256;
 void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeometry& g, const LayerCache& cache,
                      const std::vector<int>& tiling_ids, const AttentionExtras* extras = nullptr);
 

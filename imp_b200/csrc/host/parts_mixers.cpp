@@ -49,7 +49,7 @@ struct SinkBiasAttention : Mixer {
     AttentionGeometry g;
     Tensor w_qk, w_o;
     Tensor b_q, b_k, b_o, n_q, n_k, sink, bias_by_distance;   // float32
-    Tensor sink_l2, bias_l2;                                   // the last two times log2(e), for kernels that use 2^x
+    Tensor sink_l2, bias_l2, bias_pad_l2;                      // the last two times log2(e), for kernels that use 2^x; and padded
     float eps, temp_coef;
     int temp_every, n_dist;
 
@@ -126,6 +126,13 @@ struct SinkBiasAttention : Mixer {
         sink_l2 = a.store->alloc(F32, {g.hq});
         IMP_CUDA(cudaMemcpyAsync(bias_l2.data, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, rt.stream));
         IMP_CUDA(cudaMemcpyAsync(sink_l2.data, sk.data(), sk.size() * 4, cudaMemcpyHostToDevice, rt.stream));
+        // the padded layout of the tensor-memory kernel: zeros in front, the last entry repeated behind
+        const int pad = ATTENTION_BIAS_PAD, row = n_dist + 2 * pad;
+        std::vector<float> padded((size_t)g.hq * (size_t)row, 0.f);
+        for (int h = 0; h < g.hq; ++h)
+            for (int n = 0; n < n_dist + pad; ++n) padded[(size_t)h * row + pad + n] = tab[(size_t)h * n_dist + std::min(n, n_dist - 1)];
+        bias_pad_l2 = a.store->alloc(F32, {g.hq, row});
+        IMP_CUDA(cudaMemcpyAsync(bias_pad_l2.data, padded.data(), padded.size() * 4, cudaMemcpyHostToDevice, rt.stream));
         IMP_CUDA(cudaStreamSynchronize(rt.stream));
         for (const char* n : {"q_proj", "k_proj", "q_bias", "k_bias", "o_bias", "q_norm", "k_norm", "sink", "rel_bias"}) a.drop(n);
     }
@@ -153,6 +160,8 @@ struct SinkBiasAttention : Mixer {
         ex.sink = (const float*)sink.data;
         ex.bias_l2 = (const float*)bias_l2.data;
         ex.sink_l2 = (const float*)sink_l2.data;
+        ex.bias_pad_l2 = (const float*)bias_pad_l2.data;
+        ex.pad = ATTENTION_BIAS_PAD;
         paged_attention(st, attn, col_slice(qk, 0, qd), g, *cache, tiling_ids, &ex);
         Tensor out = rt.empty(T, rows(w_o));
         linear(rt, out, attn, w_o);

@@ -199,14 +199,23 @@ struct FaItem {
     bool geometry_ok;
 };
 
-template <int NQ>
+// BIAS: scores get a bias by distance and query head, and the softmax denominator one more term per head (a sink).
+// Both tables come in the log2 domain (times log2 e).  bias_pad: [Hq, FA_BIAS_PAD + n_dist + FA_BIAS_PAD], the table by
+// distance with FA_BIAS_PAD entries in front (distances below zero: keys in the future, masked) and behind (copies of the
+// last entry), so that a thread reads its row's 128 distances of a tile at fixed offsets from one pointer and never clamps;
+// a tile whose every distance lies at or beyond the table's end adds the last entry as a constant.
+constexpr int FA_BIAS_PAD = 256;
+
+template <int NQ, bool BIAS = false>
 __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, int out_tma,
     __nv_bfloat16* __restrict__ out, int64_t out_stride,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
     const int* __restrict__ positions, const int* __restrict__ tile_tok0, const int* __restrict__ tile_rows, int n_tiles,
-    int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2, int window, int* status) {
+    int n_seqs, int Hq, int Hkv, int P, int num_pages, float scale_log2_in, int window, int* status,
+    const float* __restrict__ bias_pad, int n_dist, const float* __restrict__ sink_l2) {
+    const float scale_log2 = BIAS ? 1.f : scale_log2_in;     // with a bias the scores are scaled when the bias is added
     using Cfg = FaCfg<NQ>;
     constexpr int KS = Cfg::K_STAGES, VS = Cfg::V_STAGES;
     extern __shared__ unsigned char fa_smem_raw[];
@@ -462,6 +471,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         const int n_kt = it.n_kt, pos0 = it.pos0, rows = it.rows;
         const int p = pos0 + (row < rows ? row : rows - 1);  // padding rows repeat the last real row
         float m_used = -INFINITY, l = 0.f;
+        const float* bias_h = (BIAS && bias_pad) ? bias_pad + (int64_t)(it.head0 + w) * (n_dist + 2 * FA_BIAS_PAD) + FA_BIAS_PAD : nullptr;
         for (int i = 0; i < n_kt && ok; ++i, ++t_n) {
             const int k0 = (it.kt_lo + i) * FA_BN;
             if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 0);
@@ -481,6 +491,22 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
 #pragma unroll
             for (int c = 1; c < FA_BN / 32; ++c) tc_wait_ld_pin<false>(sr[c]);
             if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 2);
+            if (BIAS) {
+                if (bias_h && pos0 - (k0 + FA_BN - 1) < n_dist - 1) {
+                    const float* bp = bias_h + (p - k0);                 // distance of column c: p - k0 - c
+#pragma unroll
+                    for (int c = 0; c < FA_BN / 32; ++c)
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            sr[c][j] = __float_as_uint(fmaf(__uint_as_float(sr[c][j]), scale_log2_in, bp[-(c * 32 + j)]));
+                } else {
+                    const float far = bias_h ? bias_h[n_dist - 1] : 0.f;  // every distance of the tile reads the last entry
+#pragma unroll
+                    for (int c = 0; c < FA_BN / 32; ++c)
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sr[c][j] = __float_as_uint(fmaf(__uint_as_float(sr[c][j]), scale_log2_in, far));
+                }
+            }
             // four independent maxima: one chain of 128 dependent comparisons would sit on the critical path
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (masked) {
@@ -556,6 +582,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         // The item's result.  The loads of O are complete (tc_ld32 waits) before this warp signals its next P, and the
         // first P V of the next item, which overwrites O, waits for that signal of all four warps.
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done0 + 8 * w, (uint32_t)(t_n - 1) & 1u, status));
+        if (BIAS && sink_l2 && m_used != -INFINITY) l += fa_exp2(sink_l2[it.head0 + w] - m_used);   // the sink: no key, no value
         if (out_tma) {
             // the head's four warps meet at barriers below: they go on, or give up, together (a warp that gave up
             // inside the item arrives here too, the others after their own waits have run out)
@@ -675,16 +702,17 @@ IMP_API int imp_attn_prefill_tc_supported(int64_t q_stride, int64_t out_stride, 
            q_stride % 8 == 0 && out_stride % 8 == 0;
 }
 
-template <int NQ>
+template <int NQ, bool BIAS = false>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, int out_tma,
                      __nv_bfloat16* out, int64_t out_stride,
                      const int* block_table, int bt_stride, const int* seq_of_token, const int* positions,
                      const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs, int Hq, int Hkv, int P,
-                     int num_pages, float scale_log2, int window, int* status, cudaStream_t s) {
+                     int num_pages, float scale_log2, int window, int* status, cudaStream_t s, const float* bias_pad = nullptr,
+                     int n_dist = 0, const float* sink_l2 = nullptr) {
     using Cfg = FaCfg<NQ>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<NQ, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::SMEM_BYTES);
         if (e != cudaSuccess) { imp_set_error("imp_attn_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
         attr_set = true;
@@ -698,19 +726,20 @@ static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
             sms = 1;
     }
     const int64_t grid = items < sms ? items : sms;
-    cudaError_t e = imp_launch(attn_prefill_tc_kernel<NQ>, dim3((unsigned)grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, s, mq, mk,
+    cudaError_t e = imp_launch(attn_prefill_tc_kernel<NQ, BIAS>, dim3((unsigned)grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, s, mq, mk,
                                mv, mo, out_tma, out, out_stride, block_table, bt_stride, seq_of_token, positions, tile_tok0, tile_rows,
-                               n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, status);
+                               n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale_log2, window, status, bias_pad, n_dist, sink_l2);
     if (e != cudaSuccess) { imp_set_error("imp_attn_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
 
 // out, q: [n_tokens, stride] bfloat16 (head h at column h*DH).  kc, vc: [num_pages, Hkv, P, DH] of one layer.
 // tile_tok0 / tile_rows: tiles of up to 128 consecutive tokens of one sequence (first row in q/out, row count).
-IMP_API int imp_attn_prefill_tc(void* out, int64_t out_stride, const void* q, int64_t q_stride, int n_tokens, const void* kc,
-                                const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
-                                const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs,
-                                int Hq, int Hkv, int P, int num_pages, float scale, int window, int* status, void* stream) {
+static int fa_prefill(void* out, int64_t out_stride, const void* q, int64_t q_stride, int n_tokens, const void* kc,
+                      const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                      const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs,
+                      int Hq, int Hkv, int P, int num_pages, float scale, int window, int* status, void* stream, bool with_bias,
+                      const float* bias_pad, int n_dist, const float* sink_l2) {
     if (n_tiles == 0) return 0;
     IMP_CHECK_ARG(out && q && kc && vc && block_table && seq_of_token && positions && tile_tok0 && tile_rows,
                   "imp_attn_prefill_tc: null pointer");
@@ -751,7 +780,36 @@ IMP_API int imp_attn_prefill_tc(void* out, int64_t out_stride, const void* q, in
         pair_min_items = e ? atoi(e) : sms / 2 + 1;
     }
     const int64_t pair_items = (int64_t)n_tiles * Hkv * ((Hq / Hkv) / 2);
-    if ((Hq / Hkv) % 2 == 0 && pair_items >= pair_min_items) return fa_launch<2>(FA_ARGS);
+    const bool pairs = (Hq / Hkv) % 2 == 0 && pair_items >= pair_min_items;
+    if (with_bias) {
+        if (pairs) return fa_launch<2, true>(FA_ARGS, bias_pad, n_dist, sink_l2);
+        return fa_launch<1, true>(FA_ARGS, bias_pad, n_dist, sink_l2);
+    }
+    if (pairs) return fa_launch<2>(FA_ARGS);
     return fa_launch<1>(FA_ARGS);
 #undef FA_ARGS
+}
+
+IMP_API int imp_attn_prefill_tc(void* out, int64_t out_stride, const void* q, int64_t q_stride, int n_tokens, const void* kc,
+                                const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                                const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs,
+                                int Hq, int Hkv, int P, int num_pages, float scale, int window, int* status, void* stream) {
+    return fa_prefill(out, out_stride, q, q_stride, n_tokens, kc, vc, block_table, bt_stride, seq_of_token, positions, tile_tok0,
+                      tile_rows, n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale, window, status, stream, false, nullptr, 0, nullptr);
+}
+
+// Entries in front of and behind each head's table by distance that imp_attn_prefill_tc_bias expects.
+IMP_API int imp_attn_prefill_tc_bias_pad(void) { return FA_BIAS_PAD; }
+
+// The same with a score bias by distance and a sink, both times log2(e): bias_pad [Hq, pad + n_dist + pad] with the
+// table's n_dist entries in the middle, zeros in front and copies of the last entry behind (pad =
+// imp_attn_prefill_tc_bias_pad()); sink_l2 [Hq].  Either may be null.
+IMP_API int imp_attn_prefill_tc_bias(void* out, int64_t out_stride, const void* q, int64_t q_stride, int n_tokens, const void* kc,
+                                     const void* vc, const int* block_table, int bt_stride, const int* seq_of_token,
+                                     const int* positions, const int* tile_tok0, const int* tile_rows, int n_tiles, int n_seqs,
+                                     int Hq, int Hkv, int P, int num_pages, float scale, int window, const float* bias_pad,
+                                     int n_dist, const float* sink_l2, int* status, void* stream) {
+    IMP_CHECK_ARG(!bias_pad || n_dist > 0, "imp_attn_prefill_tc_bias: a bias table needs at least one distance");
+    return fa_prefill(out, out_stride, q, q_stride, n_tokens, kc, vc, block_table, bt_stride, seq_of_token, positions, tile_tok0,
+                      tile_rows, n_tiles, n_seqs, Hq, Hkv, P, num_pages, scale, window, status, stream, true, bias_pad, n_dist, sink_l2);
 }
