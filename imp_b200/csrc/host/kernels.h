@@ -51,10 +51,10 @@ int imp_proj_norm_kv_write(void* qk, int64_t row_stride, int n_tokens, int Hq, i
 int imp_add_bias(void* x, int64_t stride, int n_rows, int n_cols, const float* bias, int dtype, void* stream);
 int imp_scaled_sum(void* out, const void* x, float a, const void* y, float b, const float* col_bias, float bias_scale, int n_rows,
                    int n_cols, int dtype, void* stream);
-int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, int taps, const float* conv_state, const int* seq_of_token,
+int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, int taps, float* conv_state, const int* seq_of_token,
                     const int* q_start, const int* slots, int n_tokens, int n_seqs, int G, int D, int H, int Dv, const float* a_log,
-                    const float* dt_bias, float* qn, float* kn, float* vc, float* beta, float* decay, int act_dtype, int* status,
-                    void* stream);
+                    const float* dt_bias, float* qn, float* kn, float* vc, float* beta, float* decay, int update_state, int act_dtype,
+                    int* status, void* stream);
 int imp_gdr_conv_state(const void* proj, int64_t ld, float* conv_state, int taps, int C, const int* q_start, const int* slots,
                        int n_seqs, int act_dtype, void* stream);
 int imp_gdr_scan(const float* qn, const float* kn, const float* vc, const float* beta, const float* decay, float* state, float* out,

@@ -147,6 +147,9 @@ struct Mixer : Part {
     bool defer_out = false;
     std::vector<int> tiling_ids;                         // index into Step::tiles of each declared tiling
     virtual std::vector<TilingSpec> tilings() const { return {}; }
+    // A mixer whose output ends with "+ bias" may hand that bias (float32 [hidden]) to whoever arranges it, who then adds
+    // it where it combines the output anyway; from this call on the mixer leaves it out.  Null: nothing to hand over.
+    virtual const float* defer_out_bias() { return nullptr; }
     virtual Branch forward(Step& st, Tensor x, LayerCache* cache) = 0;
     void call(Step& st, ImpCall& c) override;
 };

@@ -52,6 +52,11 @@ struct SinkBiasAttention : Mixer {
     Tensor sink_l2, bias_l2, bias_pad_l2;                      // the last two times log2(e), for kernels that use 2^x; and padded
     float eps, temp_coef;
     int temp_every, n_dist;
+    bool bias_deferred = false;
+    const float* defer_out_bias() override {
+        bias_deferred = true;
+        return (const float*)b_o.data;
+    }
 
     static TensorSpecs specs(const Json& p) {
         const char* me = "sink_bias_attention";
@@ -165,8 +170,10 @@ struct SinkBiasAttention : Mixer {
         paged_attention(st, attn, col_slice(qk, 0, qd), g, *cache, tiling_ids, &ex);
         Tensor out = rt.empty(T, rows(w_o));
         linear(rt, out, attn, w_o);
-        ++rt.launches;
-        check_launch(imp_add_bias(out.data, out.stride0, (int)T, (int)cols(out), (const float*)b_o.data, out.dtype, rt.stream), "add_bias");
+        if (!bias_deferred) {
+            ++rt.launches;
+            check_launch(imp_add_bias(out.data, out.stride0, (int)T, (int)cols(out), (const float*)b_o.data, out.dtype, rt.stream), "add_bias");
+        }
         return Branch::of(out);
     }
 };
@@ -269,14 +276,17 @@ struct GatedDeltaRule : Mixer {
         float* o = rt.arena->take<float>((size_t)T * H * Dv);
         float* S = (float*)cache->view.states[0].data;
         float* conv_state = (float*)cache->view.states[1].data;
-        rt.launches += 4;
+        // a step of single tokens: the convolution's state is rewritten by the kernel that reads it
+        const bool single = st.decode_only();
+        rt.launches += single ? 3 : 4;
         check_launch(imp_gdr_prepare(proj.data, proj.stride0, (const float*)conv_w.data, taps, conv_state, st.view.seq_of_token, st.view.q_start,
                                      st.view.state_slots, (int)T, st.B(), G, D, H, Dv, (const float*)a_log.data, (const float*)dt_bias.data, qn,
-                                     kn, vc, beta, decay, rt.dtype, rt.status, rt.stream),
+                                     kn, vc, beta, decay, single ? 1 : 0, rt.dtype, rt.status, rt.stream),
                      "gdr_prepare");
-        check_launch(imp_gdr_conv_state(proj.data, proj.stride0, conv_state, taps, C, st.view.q_start, st.view.state_slots, st.B(), rt.dtype,
-                                        rt.stream),
-                     "gdr_conv_state");
+        if (!single)
+            check_launch(imp_gdr_conv_state(proj.data, proj.stride0, conv_state, taps, C, st.view.q_start, st.view.state_slots, st.B(), rt.dtype,
+                                            rt.stream),
+                         "gdr_conv_state");
         check_launch(imp_gdr_scan(qn, kn, vc, beta, decay, S, o, st.view.q_start, st.view.state_slots, st.B(), G, D, H, Dv, rt.stream), "gdr_scan");
         Tensor y = rt.empty(T, (int64_t)H * Dv);
         const Tensor gate = col_slice(proj, C, (int64_t)H * Dv);
@@ -298,10 +308,12 @@ struct ParallelPreNormBlock : Block {
     FeedForward* ffn = nullptr;
     Norm *norm1, *norm2 = nullptr;
     float ls, rs;
+    const float* left_bias = nullptr;      // the left mixer's output bias, added (times left_scale) where the two outputs are summed
     explicit ParallelPreNormBlock(BuildArgs& a)
         : left(part_cast<Mixer>(a.part("left"), "a mixer")), right(part_cast<Mixer>(a.part("right"), "a mixer")),
           norm1(part_cast<Norm>(a.part("mixer_norm"), "a norm")), ls((float)a.params.get_double("left_scale", 1.0)),
           rs((float)a.params.get_double("right_scale", 1.0)) {
+        left_bias = left->defer_out_bias();
         if (a.params.get_bool("has_ffn", true)) {
             ffn = part_cast<FeedForward>(a.part("feed_forward"), "a feed-forward");
             norm2 = part_cast<Norm>(a.part("ffn_norm"), "a norm");
@@ -339,7 +351,7 @@ struct ParallelPreNormBlock : Block {
         Tensor b = summed(st, right->forward(st, x, cache[1].view.kind ? &cache[1] : nullptr));
         Tensor sum = rt.empty(rows(a), cols(a));
         ++rt.launches;
-        check_launch(imp_scaled_sum(sum.data, a.data, ls, b.data, rs, nullptr, 0.f, (int)rows(a), (int)cols(a), sum.dtype, rt.stream), "scaled_sum");
+        check_launch(imp_scaled_sum(sum.data, a.data, ls, b.data, rs, left_bias, ls, (int)rows(a), (int)cols(a), sum.dtype, rt.stream), "scaled_sum");
         stage(st, "mixer", sum);
         if (!ffn) return Branch::of(sum);
         x = norm2->add_norm(st, h, Branch::of(sum));
