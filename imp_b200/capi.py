@@ -195,6 +195,7 @@ _SIGNATURES = {
     "imp_config_parse": (_E, [c_char_p, c_char_p, POINTER(c_char_p)]),
     "imp_plan_for_config": (_E, [c_char_p, POINTER(c_char_p)]),
     "imp_plan_expected_tensors": (_E, [c_char_p, POINTER(c_char_p)]),
+    "imp_mixer_cache_spec": (_E, [c_char_p, c_char_p, POINTER(c_char_p)]),
     "imp_set_variant_resolver": (None, [RESOLVER_FN]),
     # single parts
     "imp_bench_create": (_E, [c_int, c_int, c_char_p, c_int, c_int, c_int, c_int, c_int, POINTER(_H)]),

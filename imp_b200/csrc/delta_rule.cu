@@ -10,8 +10,8 @@
 //   gdr_prepare     one CTA per token and head: convolution + silu of its channels, unit q and k; beta and decay
 //   gdr_conv_state  the last taps - 1 inputs of every sequence of the batch go to its state slot
 //   gdr_scan        the recurrence; a CTA owns 32 value columns of one head of one sequence and walks
-//                   the sequence's new tokens in order; four lanes share a column, each holding a
-//                   quarter of it in registers, so no state travels between tokens but through registers;
+//                   the sequence's new tokens in order; eight lanes share a column, each holding an
+//                   eighth of it in registers, so no state travels between tokens but through registers;
 //                   the tokens' inputs arrive through a two-deep cp.async ring
 //   gdr_output      per head: o / rms(o) * w * silu(gate)
 // Every column of S evolves independently of the others, which is what the scan kernel's split rests on.
@@ -119,7 +119,7 @@ __global__ void gdr_conv_state_kernel(const TA* __restrict__ proj, int64_t ld, f
 
 // ---------------------------------------------------------------------------------------- scan
 constexpr int GS_COLS = 32;          // value columns per CTA
-constexpr int GS_LANES = 4;          // lanes that share a column
+constexpr int GS_LANES = 8;          // lanes that share a column
 constexpr int GS_BLOCK = GS_COLS * GS_LANES;
 
 __device__ __forceinline__ void gs_cp_async16(void* dst, const void* src, bool valid) {
@@ -131,8 +131,14 @@ __device__ __forceinline__ void gs_cp_async4(void* dst, const void* src, bool va
                  "r"(valid ? 4 : 0) : "memory");
 }
 
-// DPL: key dimensions per lane (D <= 4 * DPL).  Lane r of a column holds dimensions [r * DPL, (r + 1) * DPL) of its
-// column of S in registers.  The new tokens' q, k, v, decay and beta travel through a two-deep ring of chunks in shared
+// DPL: key dimensions per lane (D <= 8 * DPL).  Lane r of a column holds dimensions [r * DPL, (r + 1) * DPL) of its
+// column of S in registers.  (Eight lanes a column: with four, a CTA's four warps had a scheduler each and every
+// dependent instruction waited out its latency, 730 cycles a token at D = 128; two warps a scheduler hide part of it.)
+//
+// The state's layout in memory is this kernel's own: per (slot, head, block of 32 columns) DPL planes of 256 floats,
+// plane i holding element (dimension r * DPL + i, column c) at c * 8 + r, which is the thread's own index.  A warp so
+// reads and writes 128 contiguous bytes per plane, and dimensions beyond D and columns beyond Dv are zeros that stay
+// zeros.  imp_gdr_state_floats() gives the size per slot.  The new tokens' q, k, v, decay and beta travel through a two-deep ring of chunks in shared
 // memory (cp.async; the next chunk is on its way while this one is computed); outputs leave a chunk at a time.
 //
 // Per token, with a = S^T k, c = S^T q (both on the state before the token) and kq = k . q:
@@ -140,40 +146,37 @@ __device__ __forceinline__ void gs_cp_async4(void* dst, const void* src, bool va
 // which is the recurrence's read-out S_new^T q written so that both reductions over the key dimension start from
 // the old state at once: one round of shuffles per token on the critical path instead of two.
 template <int DPL, bool VEC>
-__global__ void __launch_bounds__(GS_BLOCK) gdr_scan_kernel(
+__global__ void __launch_bounds__(GS_BLOCK, 1) gdr_scan_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc, const float* __restrict__ beta,
     const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out, const int* __restrict__ q_start,
     const int* __restrict__ slots, int G, int D, int H, int Dv) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int ROW = DPL + 4;                          // padded so that the four lanes' 16-byte reads miss each other's banks
-    constexpr int CH = DPL <= 32 ? 16 : 8;                // tokens per chunk
+    constexpr int ROW = DPL + 4;                          // padded so that the eight lanes' 16-byte reads miss each other's banks
+    constexpr int CH = DPL <= 16 ? 16 : 8;                // tokens per chunk
     __shared__ __align__(16) float k_s[2][CH][GS_LANES * ROW];
     __shared__ __align__(16) float q_s[2][CH][GS_LANES * ROW];
     __shared__ float v_s[2][CH][GS_COLS];
     __shared__ float g_s[2][CH], b_s[2][CH];
     __shared__ float o_s[CH][GS_COLS];
-    const int tid = threadIdx.x, r = tid & (GS_LANES - 1), ci = tid >> 2;
-    const int col0 = blockIdx.x * GS_COLS, col = col0 + ci;
+    const int tid = threadIdx.x, r = tid & (GS_LANES - 1), ci = tid / GS_LANES;
+    const int col0 = blockIdx.x * GS_COLS;
     const int h = blockIdx.y, seq = blockIdx.z;
     const int hk = h / (H / G);
     const int start = q_start[seq], n = q_start[seq + 1] - start;
     if (n <= 0) return;
-    const bool live = col < Dv;
-    float* S = state + (((int64_t)slots[seq] * H + h) * D) * Dv + col;
+    float* S = state + ((((int64_t)slots[seq] * H + h) * gridDim.x + blockIdx.x) * DPL) * GS_BLOCK + tid;
     float s[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        const int d = r * DPL + i;
-        s[i] = (live && d < D) ? S[(int64_t)d * Dv] : 0.f;
-    }
+    for (int i = 0; i < DPL; ++i) s[i] = S[i * GS_BLOCK];
     const int nqk = G * D;
     const int64_t hv = (int64_t)H * Dv;
     auto load_chunk = [&](int t0, int buf) {
         const int nt = min(CH, n - t0);
         if (VEC) {
-            for (int e = tid; e < CH * DPL; e += GS_BLOCK) {          // 16 bytes = 4 dimensions, all inside one lane's run
-                const int tt = e / DPL, d = (e - tt * DPL) * 4;
+            constexpr int V4 = GS_LANES * DPL / 4;                      // 16-byte pieces of a (padded) row: 4 dimensions, all inside one lane's run
+            for (int e = tid; e < CH * V4; e += GS_BLOCK) {
+                const int tt = e / V4, d = (e - tt * V4) * 4;
                 const bool ok = tt < nt && d < D;
                 const int64_t src = ok ? (int64_t)(start + t0 + tt) * nqk + hk * D + d : 0;
                 const int dst = (d / DPL) * ROW + d % DPL;
@@ -236,6 +239,9 @@ __global__ void __launch_bounds__(GS_BLOCK) gdr_scan_kernel(
             a += __shfl_xor_sync(0xffffffffu, a, 2);
             c += __shfl_xor_sync(0xffffffffu, c, 2);
             kq += __shfl_xor_sync(0xffffffffu, kq, 2);
+            a += __shfl_xor_sync(0xffffffffu, a, 4);
+            c += __shfl_xor_sync(0xffffffffu, c, 4);
+            kq += __shfl_xor_sync(0xffffffffu, kq, 4);
             const float u = b * (v - g * a);
 #pragma unroll
             for (int i = 0; i < DPL / 4; ++i) {
@@ -254,10 +260,7 @@ __global__ void __launch_bounds__(GS_BLOCK) gdr_scan_kernel(
         }
     }
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        const int d = r * DPL + i;
-        if (live && d < D) S[(int64_t)d * Dv] = s[i];
-    }
+    for (int i = 0; i < DPL; ++i) S[i * GS_BLOCK] = s[i];
 }
 
 // -------------------------------------------------------------------------------------- output
@@ -326,7 +329,16 @@ IMP_API int imp_gdr_conv_state(const void* proj, int64_t ld, float* conv_state, 
     IMP_RETURN_LAUNCH();
 }
 
-// state: [slots, H, D, Dv] float32, updated in place; out: [n_tokens, H * Dv] float32.
+// Key dimensions a lane holds for key size D (eight lanes a column).
+static int gdr_dims_per_lane(int D) { return D <= 32 ? 4 : D <= 64 ? 8 : D <= 128 ? 16 : 32; }
+
+// Floats of one request's state S for H heads of D x Dv in the scan kernel's layout (padded to whole lanes and column blocks).
+IMP_API int64_t imp_gdr_state_floats(int H, int D, int Dv) {
+    return (int64_t)H * ((Dv + GS_COLS - 1) / GS_COLS) * gdr_dims_per_lane(D) * GS_BLOCK;
+}
+
+// state: [slots, imp_gdr_state_floats(H, D, Dv)] float32 in the kernel's own layout, zero at a request's start, updated in
+// place; out: [n_tokens, H * Dv] float32.
 IMP_API int imp_gdr_scan(const float* qn, const float* kn, const float* vc, const float* beta, const float* decay, float* state,
                          float* out, const int* q_start, const int* slots, int n_seqs, int G, int D, int H, int Dv, void* stream) {
     if (n_seqs == 0) return 0;
@@ -345,11 +357,12 @@ IMP_API int imp_gdr_scan(const float* qn, const float* kn, const float* vc, cons
         if (vec) imp_launch(gdr_scan_kernel<DPL, true>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv); \
         else imp_launch(gdr_scan_kernel<DPL, false>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv);    \
     } while (0)
-    if (D <= 16) GDR_SCAN(4);
-    else if (D <= 32) GDR_SCAN(8);
-    else if (D <= 64) GDR_SCAN(16);
-    else if (D <= 128) GDR_SCAN(32);
-    else GDR_SCAN(64);
+    switch (gdr_dims_per_lane(D)) {
+        case 4: GDR_SCAN(4); break;
+        case 8: GDR_SCAN(8); break;
+        case 16: GDR_SCAN(16); break;
+        default: GDR_SCAN(32); break;
+    }
 #undef GDR_SCAN
     IMP_RETURN_LAUNCH();
 }

@@ -526,6 +526,17 @@ IMP_EXPORT ImpError imp_plan_expected_tensors(const char* plan_json, const char*
     IMP_CATCH
 }
 
+IMP_EXPORT ImpError imp_mixer_cache_spec(const char* kind, const char* params_json, const char** out_json) {
+    IMP_TRY
+    need_arg(kind && out_json, "imp_mixer_cache_spec: kind and out_json must not be null");
+    ensure_builtin_parts();
+    const PartClass& cls = part_class("mixer", kind);
+    const Json params = params_json ? Json::parse(params_json, "params") : Json::object();
+    g_text = (cls.cache_spec ? cls.cache_spec(params) : CacheSpec()).to_json().dump();
+    *out_json = g_text.c_str();
+    IMP_CATCH
+}
+
 IMP_EXPORT void imp_set_variant_resolver(const char* (*fn)(const char*, int)) { set_variant_resolver(fn); }
 
 // --------------------------------------------------------- single parts and a bare step function

@@ -57,6 +57,7 @@ int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, int taps,
                     int* status, void* stream);
 int imp_gdr_conv_state(const void* proj, int64_t ld, float* conv_state, int taps, int C, const int* q_start, const int* slots,
                        int n_seqs, int act_dtype, void* stream);
+int64_t imp_gdr_state_floats(int H, int D, int Dv);
 int imp_gdr_scan(const float* qn, const float* kn, const float* vc, const float* beta, const float* decay, float* state, float* out,
                  const int* q_start, const int* slots, int n_seqs, int G, int D, int H, int Dv, void* stream);
 int imp_gdr_output(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, float eps, int n_tokens, int H, int Dv,

@@ -184,7 +184,8 @@ struct SinkBiasAttention : Mixer {
 //   q, k unit vectors per head, q times D^(-1/2); beta = sigmoid(Wb x); decay = exp(-exp(A_log) softplus(Wa x + dt_bias));
 //   o = recurrence; y = o / rms(o) * w_norm * silu(Wg x) per head; out = Wo y.
 // One product makes q, k, v, the gate, beta's and the decay's inputs; its rows are padded to a multiple of 8.
-// State per request: S [H, D, Dv] and the last conv_taps - 1 inputs of the convolution, both float32.
+// State per request: S (H heads of D x Dv, in the scan kernel's layout) and the last conv_taps - 1 inputs of the
+// convolution, both float32.
 //
 // params: hidden_size, num_heads, num_kv_heads, key_dim, value_dim, conv_taps, norm_eps.
 struct GatedDeltaRule : Mixer {
@@ -227,7 +228,8 @@ struct GatedDeltaRule : Mixer {
         const Sizes z = sizes(p);
         CacheSpec s;
         s.kind = CacheSpec::State;
-        s.states.push_back(StateTensorSpec{"S", {z.H, z.D, z.Dv}, F32});
+        // S in the scan kernel's own layout (whole lanes and column blocks; see csrc/delta_rule.cu)
+        s.states.push_back(StateTensorSpec{"S", {imp_gdr_state_floats((int)z.H, (int)z.D, (int)z.Dv)}, F32});
         s.states.push_back(StateTensorSpec{"conv", {std::max<int64_t>(z.taps - 1, 1), z.channels()}, F32});
         return s;
     }

@@ -29,3 +29,8 @@ def unregister_part(category: str, kind: str) -> None:
 
 def known_parts(category: str):
     return sorted(json.loads(capi.text(capi.load().imp_known_parts(category.encode()))))
+
+
+def mixer_cache_spec(kind: str, params: dict):
+    """The cache spec (a JSON dictionary, or None) a mixer kind asks for with these parameters."""
+    return capi.call_json(capi.load().imp_mixer_cache_spec, kind.encode(), json.dumps(params).encode())

@@ -142,6 +142,9 @@ IMP_EXPORT const char* imp_known_architectures(void);           /* JSON list */
 /* The validated, typed configuration of a config.json text, and the plan its architecture gives. */
 IMP_EXPORT ImpError imp_config_parse(const char* config_json, const char* where, const char** out_json);
 IMP_EXPORT ImpError imp_plan_for_config(const char* config_json, const char** out_json);
+/* The cache spec JSON (null: none) a mixer kind asks for with these parameters: what a cache manager or a part bench
+ * has to be built with to run that mixer alone. */
+IMP_EXPORT ImpError imp_mixer_cache_spec(const char* kind, const char* params_json, const char** out_json);
 /* Checkpoint tensor name -> spec JSON, over all parts of a plan. */
 IMP_EXPORT ImpError imp_plan_expected_tensors(const char* plan_json, const char** out_json);
 

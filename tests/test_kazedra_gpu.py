@@ -10,9 +10,10 @@ import numpy as np
 import pytest
 import torch
 
-from imp_b200.cache.manager import PagedKVSpec, StateSpec
+from imp_b200.cache.manager import PagedKVSpec
 from imp_b200.parts.bench import PartBench
 from imp_b200.parts.plan import PartSpec
+from imp_b200.parts.registry import mixer_cache_spec
 from plain import kazedra_plain as K
 from replay_helpers import collect, mixed, portions, round64, run_trace, tail_decode, whole
 from safetensors_io import save_safetensors
@@ -198,12 +199,11 @@ RIGHT_CASES = [
 
 def right_setup(dtype, case, slots=4):
     c = {k: case[k] for k in ("heads", "kv_heads", "dim", "vdim", "conv")}
-    C = 2 * c["kv_heads"] * c["dim"] + c["heads"] * c["vdim"]
-    spec = StateSpec(tensors=(("S", (c["heads"], c["dim"], c["vdim"]), "float32"), ("conv", (max(c["conv"] - 1, 1), C), "float32")))
-    bench = PartBench(NAME[dtype], [spec], slots=slots, max_tokens=512, max_seq_len=512)
-    w = {k: v.to(dtype) for k, v in right_weights(case["d"], c, seed=200).items()}
     params = {"hidden_size": case["d"], "num_heads": c["heads"], "num_kv_heads": c["kv_heads"], "key_dim": c["dim"],
               "value_dim": c["vdim"], "conv_taps": c["conv"], "norm_eps": 2e-5}
+    # the state this mixer asks for (S in its scan kernel's layout, and the convolution's last inputs)
+    bench = PartBench(NAME[dtype], [mixer_cache_spec("gated_delta_rule", params)], slots=slots, max_tokens=512, max_seq_len=512)
+    w = {k: v.to(dtype) for k, v in right_weights(case["d"], c, seed=200).items()}
     part = bench.build("mixer", PartSpec("gated_delta_rule", params), {RIGHT_NAMES[k]: v.to(DEV) for k, v in w.items()})
     return bench, part, c, {"m." + k: v.double() for k, v in w.items()}
 
