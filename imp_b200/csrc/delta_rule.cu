@@ -7,7 +7,7 @@
 // state) followed by silu; q and k are then unit vectors per head and q carries D^(-1/2).
 //
 // Four kernels, all 32-bit arithmetic on 32-bit state whatever the activation type:
-//   gdr_prepare     one CTA per token and head: convolution + silu of its channels, unit q and k; beta and decay
+//   gdr_prepare     one warp per token and head: convolution + silu of its channels, unit q and k; beta and decay
 //   gdr_conv_state  the last taps - 1 inputs of every sequence of the batch go to its state slot
 //   gdr_scan        the recurrence; a CTA owns 32 value columns of one head of one sequence and walks
 //                   the sequence's new tokens in order; eight lanes share a column, each holding an
@@ -26,9 +26,9 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // proj: [T, ld] activations, columns [q: G*D | k: G*D | v: H*Dv | gate: H*Dv | b: H | a: H].
 // conv_w: [C, taps] float32 with C = 2*G*D + H*Dv (the last tap is the current token's).
 // conv_state: [slots, taps - 1, C] float32: the inputs of the taps - 1 tokens before the portion.
-// grid (2G + H + 1, T): a CTA makes one head of one token (a q head, a k head or a v head: convolution, silu, and
-// for q and k the unit norm), the last CTA of a token its H step sizes and decays.  So a decode step of a few
-// tokens still spreads over the device.
+// A warp makes one head of one token (a q head, a k head or a v head: convolution, silu, and for q and k the unit
+// norm, summed inside the warp), or a token's H step sizes and decays; a CTA holds four warps and there are no
+// block-wide steps, so a decode step of a few tokens still spreads over the device and a prompt's rows stream.
 constexpr int GP_BLOCK = 128;
 constexpr int GP_MAX_D = 256;
 
@@ -37,65 +37,64 @@ __global__ void __launch_bounds__(GP_BLOCK) gdr_prepare_kernel(
     const TA* __restrict__ proj, int64_t ld, const float* __restrict__ conv_w, int taps, float* __restrict__ conv_state,
     const int* __restrict__ seq_of_token, const int* __restrict__ q_start, const int* __restrict__ slots, int n_tokens, int n_seqs,
     int G, int D, int H, int Dv, const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* __restrict__ qn,
-    float* __restrict__ kn, float* __restrict__ vc, float* __restrict__ beta, float* __restrict__ decay, int tokens_per_cta,
-    int update_state, int* status) {
+    float* __restrict__ kn, float* __restrict__ vc, float* __restrict__ beta, float* __restrict__ decay, int update_state, int* status) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float scratch[33];
-    const int unit = blockIdx.x, tid = threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int units = 2 * G + H + 1;
+    const int64_t item = (int64_t)blockIdx.x * (GP_BLOCK / 32) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_tokens * units) return;
+    const int t = (int)(item / units), unit = (int)(item - (int64_t)t * units);
     const int nqk = G * D, C = 2 * nqk + H * Dv;
-    const int t_end = min(n_tokens, ((int)blockIdx.y + 1) * tokens_per_cta);
-    for (int t = blockIdx.y * tokens_per_cta; t < t_end; ++t) {
-        const int seq = seq_of_token[t];
-        if (seq < 0 || seq >= n_seqs) {
-            if (tid == 0 && unit == 0) imp_report(status, IMP_BAD_SEQUENCE);
-            continue;
+    const int seq = seq_of_token[t];
+    if (seq < 0 || seq >= n_seqs) {
+        if (lane == 0 && unit == 0) imp_report(status, IMP_BAD_SEQUENCE);
+        return;
+    }
+    if (unit == 2 * G + H) {
+        for (int hh = lane; hh < H; hh += 32) {
+            const TA* row = proj + (int64_t)t * ld + C + H * Dv;
+            const float b = to_float(row[hh]), a = to_float(row[H + hh]);
+            beta[(int64_t)t * H + hh] = 1.f / (1.f + expf(-b));
+            decay[(int64_t)t * H + hh] = expf(-expf(a_log[hh]) * softplus_f(a + dt_bias[hh]));
         }
-        if (unit == 2 * G + H) {
-            for (int hh = tid; hh < H; hh += GP_BLOCK) {
-                const TA* row = proj + (int64_t)t * ld + C + H * Dv;
-                const float b = to_float(row[hh]), a = to_float(row[H + hh]);
-                beta[(int64_t)t * H + hh] = 1.f / (1.f + expf(-b));
-                decay[(int64_t)t * H + hh] = expf(-expf(a_log[hh]) * softplus_f(a + dt_bias[hh]));
-            }
-            continue;
+        return;
+    }
+    const int start = q_start[seq];
+    const int n = t - start;                 // index of the token inside its portion
+    float* st = conv_state + (int64_t)slots[seq] * (taps - 1) * C;
+    // update_state (every sequence of the step brings one token): the thread that read a channel's earlier inputs
+    // also shifts them down and appends the new one, and no separate pass over the state is needed
+    auto channel = [&](int c) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int idx = n - (taps - 1) + j;
+            const float x = idx >= 0 ? to_float(proj[(int64_t)(start + idx) * ld + c]) : st[(int64_t)(taps - 1 + idx) * C + c];
+            if (update_state && j >= 1) st[(int64_t)(j - 1) * C + c] = x;
+            acc = fmaf(conv_w[(int64_t)c * taps + j], x, acc);
         }
-        const int start = q_start[seq];
-        const int n = t - start;                 // index of the token inside its portion
-        float* st = conv_state + (int64_t)slots[seq] * (taps - 1) * C;
-        // update_state (every sequence of the step brings one token): the thread that read a channel's earlier inputs
-        // also shifts them down and appends the new one, and no separate pass over the state is needed
-        auto channel = [&](int c) {
-            float acc = 0.f;
-            for (int j = 0; j < taps; ++j) {
-                const int idx = n - (taps - 1) + j;
-                const float x = idx >= 0 ? to_float(proj[(int64_t)(start + idx) * ld + c]) : st[(int64_t)(taps - 1 + idx) * C + c];
-                if (update_state && j >= 1) st[(int64_t)(j - 1) * C + c] = x;
-                acc = fmaf(conv_w[(int64_t)c * taps + j], x, acc);
-            }
-            return silu_f(acc);
-        };
-        if (unit >= 2 * G) {                     // a value head: no norm
-            const int hh = unit - 2 * G;
-            for (int d = tid; d < Dv; d += GP_BLOCK) vc[(int64_t)t * H * Dv + hh * Dv + d] = channel(2 * nqk + hh * Dv + d);
-            continue;
-        }
-        // a q or k head: at most two channels a thread, unit norm over the head
-        float x[GP_MAX_D / GP_BLOCK], ss = 0.f;
+        return silu_f(acc);
+    };
+    if (unit >= 2 * G) {                     // a value head: no norm
+        const int hh = unit - 2 * G;
+        for (int d = lane; d < Dv; d += 32) vc[(int64_t)t * H * Dv + hh * Dv + d] = channel(2 * nqk + hh * Dv + d);
+        return;
+    }
+    // a q or k head: up to eight channels a lane, unit norm over the head
+    float x[GP_MAX_D / 32], ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < GP_MAX_D / GP_BLOCK; ++i) {
-            const int d = tid + i * GP_BLOCK;
-            x[i] = d < D ? channel(unit * D + d) : 0.f;
-            ss = fmaf(x[i], x[i], ss);
-        }
-        ss = block_sum(ss, scratch);
-        const float r = rsqrtf(ss + 1e-6f) * (unit < G ? rsqrtf((float)D) : 1.f);
-        float* dst = unit < G ? qn + (int64_t)t * nqk + unit * D : kn + (int64_t)t * nqk + (unit - G) * D;
+    for (int i = 0; i < GP_MAX_D / 32; ++i) {
+        const int d = lane + i * 32;
+        x[i] = d < D ? channel(unit * D + d) : 0.f;
+        ss = fmaf(x[i], x[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss + 1e-6f) * (unit < G ? rsqrtf((float)D) : 1.f);
+    float* dst = unit < G ? qn + (int64_t)t * nqk + unit * D : kn + (int64_t)t * nqk + (unit - G) * D;
 #pragma unroll
-        for (int i = 0; i < GP_MAX_D / GP_BLOCK; ++i) {
-            const int d = tid + i * GP_BLOCK;
-            if (d < D) dst[d] = x[i] * r;
-        }
+    for (int i = 0; i < GP_MAX_D / 32; ++i) {
+        const int d = lane + i * 32;
+        if (d < D) dst[d] = x[i] * r;
     }
 }
 
@@ -298,20 +297,18 @@ IMP_API int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, i
     IMP_CHECK_ARG(G > 0 && H > 0 && H % G == 0 && D > 0 && D <= GP_MAX_D && Dv > 0 && taps >= 1,
                   "imp_gdr_prepare: bad sizes (heads %d over %d key heads, key size %d of at most %d)", H, G, D, GP_MAX_D);
     IMP_CHECK_ARG(!update_state || n_tokens == n_seqs, "imp_gdr_prepare: the state is updated in place only when every sequence brings one token");
-    // long batches: a CTA walks several tokens, so that the grid stays within bounds and a CTA's start is paid once
-    const int tokens_per_cta = n_tokens >= 1024 ? 4 : 1;
-    const int C = 2 * G * D + H * Dv;
-    IMP_CHECK_ARG(ld >= (int64_t)C + H * Dv + 2 * H, "imp_gdr_prepare: the projection's rows are too short");
+    IMP_CHECK_ARG(ld >= (int64_t)2 * G * D + 2 * (int64_t)H * Dv + 2 * H, "imp_gdr_prepare: the projection's rows are too short");
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(2 * G + H + 1, (n_tokens + tokens_per_cta - 1) / tokens_per_cta);
-    IMP_CHECK_ARG(grid.y <= 65535, "imp_gdr_prepare: too many tokens");
+    const int64_t items = (int64_t)n_tokens * (2 * G + H + 1);
+    const int64_t ctas = (items + GP_BLOCK / 32 - 1) / (GP_BLOCK / 32);
+    IMP_CHECK_ARG(ctas <= 0x7fffffff, "imp_gdr_prepare: too many tokens");
+    const dim3 grid((unsigned)ctas);
     if (act_dtype == IMP_F32)
         imp_launch(gdr_prepare_kernel<float>, grid, dim3(GP_BLOCK), 0, s, (const float*)proj, ld, conv_w, taps, conv_state, seq_of_token,
-                   q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, tokens_per_cta, update_state, status);
+                   q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, update_state, status);
     else
         imp_launch(gdr_prepare_kernel<__nv_bfloat16>, grid, dim3(GP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, conv_w, taps, conv_state,
-                   seq_of_token, q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, tokens_per_cta,
-                   update_state, status);
+                   seq_of_token, q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, update_state, status);
     IMP_RETURN_LAUNCH();
 }
 

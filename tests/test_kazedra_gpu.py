@@ -81,6 +81,7 @@ LEFT_CASES = [
     dict(heads=6, kv_heads=3, dim=24, d=72, buckets=12, bias_max=40, every=5, page=4),
     dict(heads=4, kv_heads=4, dim=40, d=48, buckets=7, bias_max=9, every=64, page=16),
     dict(heads=5, kv_heads=1, dim=64, d=80, buckets=32, bias_max=300, every=1, page=8),
+    dict(heads=12, kv_heads=1, dim=32, d=64, buckets=10, bias_max=30, every=3, page=16),     # twelve query heads on one kv head
 ]
 
 
@@ -186,6 +187,31 @@ def test_one_far_key_among_hundreds(dtype):
     x2 = x.clone()
     x2[3] = 0
     assert (K.sink_bias_attention(x2.double(), W, "m.", c, 1e-6)[405] - want[405]).abs().max() > 0.3 * want[405].abs().max()
+
+
+def test_long_prompt_on_wide_heads():
+    """Head size 128, four query heads per kv head, 1,200 tokens: enough work items that the tensor-memory kernel takes two
+    query heads per item; a table shorter than the prompt, so that early tiles of late rows add its last entry."""
+    case = dict(heads=16, kv_heads=4, dim=128, d=128, buckets=16, bias_max=300, every=64, page=16)
+    c = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "bias_max": 300, "scale": 1.3 / math.sqrt(128), "q_temp": {"coef": 0.4, "every": 64}}
+    dtype = torch.bfloat16
+    bench = PartBench("bfloat16", [PagedKVSpec(4, 128, 0)], page_size=16, num_pages=128, max_tokens=2048, max_seq_len=2048)
+    w = {k: v.to(dtype) for k, v in left_weights(128, c, 16, seed=400, strong=2.0).items()}
+    params = {"hidden_size": 128, "num_heads": 16, "num_kv_heads": 4, "head_dim": 128, "scale": c["scale"], "norm_eps": 2e-5,
+              "q_temp_coef": 0.4, "q_temp_every": 64, "bias_max_distance": 300}
+    part = bench.build("mixer", PartSpec("sink_bias_attention", params), {LEFT_NAMES[k]: v.to(DEV) for k, v in w.items()})
+    W = {"m." + k: v.double() for k, v in w.items()}
+    T = 1200
+    x = rnd(T, 128, seed=401).to(dtype)
+    want = K.sink_bias_attention(x.double(), W, "m.", c, 2e-5)
+    ctx = bench.prepare([("a", [1] * 1100, [])])
+    out = run_mixer(bench, part, x[:1100], ctx, bench.cache_view(0))
+    bench.commit()
+    close(out, want[:1100], dtype, "prompt")
+    ctx = bench.prepare([("a", [1] * 100, [])])                      # a portion that starts inside a tile, late in the sequence
+    out = run_mixer(bench, part, x[1100:], ctx, bench.cache_view(0))
+    bench.commit()
+    close(out, want[1100:], dtype, "portion")
 
 
 # ----------------------------------------------------- the recurrent mixer alone
