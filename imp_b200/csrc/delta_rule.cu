@@ -32,14 +32,16 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 constexpr int GP_BLOCK = 128;
 constexpr int GP_MAX_D = 256;
 
-template <typename TA>
+// TAPS: the convolution's taps at compile time (0: read from `taps_rt`), so that a channel's loads go out together.
+template <typename TA, int TAPS>
 __global__ void __launch_bounds__(GP_BLOCK) gdr_prepare_kernel(
-    const TA* __restrict__ proj, int64_t ld, const float* __restrict__ conv_w, int taps, float* __restrict__ conv_state,
+    const TA* __restrict__ proj, int64_t ld, const float* __restrict__ conv_w, int taps_rt, float* __restrict__ conv_state,
     const int* __restrict__ seq_of_token, const int* __restrict__ q_start, const int* __restrict__ slots, int n_tokens, int n_seqs,
     int G, int D, int H, int Dv, const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* __restrict__ qn,
     float* __restrict__ kn, float* __restrict__ vc, float* __restrict__ beta, float* __restrict__ decay, int update_state, int* status) {
     pdl_wait();
     pdl_launch_dependents();
+    const int taps = TAPS ? TAPS : taps_rt;
     const int lane = threadIdx.x & 31;
     const int units = 2 * G + H + 1;
     const int64_t item = (int64_t)blockIdx.x * (GP_BLOCK / 32) + (threadIdx.x >> 5);
@@ -67,11 +69,26 @@ __global__ void __launch_bounds__(GP_BLOCK) gdr_prepare_kernel(
     // also shifts them down and appends the new one, and no separate pass over the state is needed
     auto channel = [&](int c) {
         float acc = 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int idx = n - (taps - 1) + j;
-            const float x = idx >= 0 ? to_float(proj[(int64_t)(start + idx) * ld + c]) : st[(int64_t)(taps - 1 + idx) * C + c];
-            if (update_state && j >= 1) st[(int64_t)(j - 1) * C + c] = x;
-            acc = fmaf(conv_w[(int64_t)c * taps + j], x, acc);
+        if constexpr (TAPS > 0) {
+            float x[TAPS], w[TAPS];
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                const int idx = n - (TAPS - 1) + j;
+                x[j] = idx >= 0 ? to_float(proj[(int64_t)(start + idx) * ld + c]) : st[(int64_t)(TAPS - 1 + idx) * C + c];
+                w[j] = conv_w[(int64_t)c * TAPS + j];
+            }
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                if (update_state && j >= 1) st[(int64_t)(j - 1) * C + c] = x[j];
+                acc = fmaf(w[j], x[j], acc);
+            }
+        } else {
+            for (int j = 0; j < taps; ++j) {
+                const int idx = n - (taps - 1) + j;
+                const float x = idx >= 0 ? to_float(proj[(int64_t)(start + idx) * ld + c]) : st[(int64_t)(taps - 1 + idx) * C + c];
+                if (update_state && j >= 1) st[(int64_t)(j - 1) * C + c] = x;
+                acc = fmaf(conv_w[(int64_t)c * taps + j], x, acc);
+            }
         }
         return silu_f(acc);
     };
@@ -132,7 +149,8 @@ __device__ __forceinline__ void gs_cp_async4(void* dst, const void* src, bool va
 
 // DPL: key dimensions per lane (D <= 8 * DPL).  Lane r of a column holds dimensions [r * DPL, (r + 1) * DPL) of its
 // column of S in registers.  (Eight lanes a column: with four, a CTA's four warps had a scheduler each and every
-// dependent instruction waited out its latency, 730 cycles a token at D = 128; two warps a scheduler hide part of it.)
+// dependent instruction waited out its latency, 730 cycles a token at D = 128; two warps a scheduler hide part of it.
+// Sixteen lanes and a fourth round of shuffles measured slower again: a 2,048-token prompt of four layers 7.1 against 6.6 ms.)
 //
 // The state's layout in memory is this kernel's own: per (slot, head, block of 32 columns) DPL planes of 256 floats,
 // plane i holding element (dimension r * DPL + i, column c) at c * 8 + r, which is the thread's own index.  A warp so
@@ -303,12 +321,20 @@ IMP_API int imp_gdr_prepare(const void* proj, int64_t ld, const float* conv_w, i
     const int64_t ctas = (items + GP_BLOCK / 32 - 1) / (GP_BLOCK / 32);
     IMP_CHECK_ARG(ctas <= 0x7fffffff, "imp_gdr_prepare: too many tokens");
     const dim3 grid((unsigned)ctas);
-    if (act_dtype == IMP_F32)
-        imp_launch(gdr_prepare_kernel<float>, grid, dim3(GP_BLOCK), 0, s, (const float*)proj, ld, conv_w, taps, conv_state, seq_of_token,
-                   q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, update_state, status);
-    else
-        imp_launch(gdr_prepare_kernel<__nv_bfloat16>, grid, dim3(GP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, conv_w, taps, conv_state,
-                   seq_of_token, q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, update_state, status);
+#define GDR_PREPARE(TA, TAPS)                                                                                                      \
+    imp_launch(gdr_prepare_kernel<TA, TAPS>, grid, dim3(GP_BLOCK), 0, s, (const TA*)proj, ld, conv_w, taps, conv_state, seq_of_token, \
+               q_start, slots, n_tokens, n_seqs, G, D, H, Dv, a_log, dt_bias, qn, kn, vc, beta, decay, update_state, status)
+#define GDR_PREPARE_T(TA)                       \
+    do {                                        \
+        if (taps == 4) GDR_PREPARE(TA, 4);      \
+        else if (taps == 3) GDR_PREPARE(TA, 3); \
+        else if (taps == 2) GDR_PREPARE(TA, 2); \
+        else GDR_PREPARE(TA, 0);                \
+    } while (0)
+    if (act_dtype == IMP_F32) GDR_PREPARE_T(float);
+    else GDR_PREPARE_T(__nv_bfloat16);
+#undef GDR_PREPARE_T
+#undef GDR_PREPARE
     IMP_RETURN_LAUNCH();
 }
 
@@ -349,10 +375,13 @@ IMP_API int imp_gdr_scan(const float* qn, const float* kn, const float* vc, cons
     dim3 grid((Dv + GS_COLS - 1) / GS_COLS, H, n_seqs);
     // 16-byte copies of q and k rows need rows that start on 16 bytes: D a multiple of 4 and aligned buffers
     const bool vec = D % 4 == 0 && (uintptr_t)qn % 16 == 0 && (uintptr_t)kn % 16 == 0;
-#define GDR_SCAN(DPL)                                                                                                                  \
-    do {                                                                                                                               \
-        if (vec) imp_launch(gdr_scan_kernel<DPL, true>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv); \
-        else imp_launch(gdr_scan_kernel<DPL, false>, grid, dim3(GS_BLOCK), 0, s, qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv);    \
+    // Launched as an ordinary dependent, without the programmatic attribute: its CTAs hold three quarters of an SM's
+    // registers, and resident early (waiting for the kernels before them) they starved those kernels: a 2,048-token
+    // prompt of four layers took 8.1 instead of 6.7 ms.
+#define GDR_SCAN(DPL)                                                                                                          \
+    do {                                                                                                                       \
+        if (vec) gdr_scan_kernel<DPL, true><<<grid, GS_BLOCK, 0, s>>>(qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv); \
+        else gdr_scan_kernel<DPL, false><<<grid, GS_BLOCK, 0, s>>>(qn, kn, vc, beta, decay, state, out, q_start, slots, G, D, H, Dv);    \
     } while (0)
     switch (gdr_dims_per_lane(D)) {
         case 4: GDR_SCAN(4); break;
