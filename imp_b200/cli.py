@@ -22,7 +22,7 @@ from typing import List, Optional
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="imp-cli", description="Qwen3 dense decoder on one B200")
+    p = argparse.ArgumentParser(prog="imp-cli", description="Generate with a model folder (Qwen3 dense decoder or Kazedra) on one B200")
     p.add_argument("--model", required=True, help="model folder (config.json + model.safetensors; "
                                                   "config.json alone with --random-weights)")
     p.add_argument("--prompt", default=None, help="token ids (comma or space separated) or text taken as bytes")

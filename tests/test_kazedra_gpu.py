@@ -451,3 +451,34 @@ def test_greedy_generation_through_the_engine(kazedra_folders):
         top2 = torch.topk(lg, 2).values
         if float(top2[0] - top2[1]) > 0.1 * float(lg.abs().max()):
             assert g16[0] == w[0]
+
+
+def test_command_line_generates_the_plain_tokens(kazedra_folders, tmp_path):
+    """bin/imp-cli on a Kazedra folder: greedy tokens of the plain model; with only config.json (and the rows of the
+    distance tables named there) random weights and the bench mode run too."""
+    import subprocess
+    import sys
+    cli = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "imp-cli")
+    folder, cfg, page, W, reqs, ref = kazedra_folders["K1"]
+    ids, want = [5, 17, 3], []
+    for _ in range(6):
+        want.append(int(torch.argmax(K.forward(cfg, W, ids + want)[-1])))
+    p = subprocess.run([sys.executable, cli, "--model", folder, "--prompt", "5,17,3", "--max-tokens", "6", "--temperature", "0",
+                        "--dtype", "fp32", "--page-size", str(page), "--kv-pages", "64", "--max-seq-len", "128"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(x) for x in p.stdout.split()] == want
+    only_config = tmp_path / "cfg"
+    only_config.mkdir()
+    (only_config / "config.json").write_text(json.dumps(dict(cfg, bias_buckets=8)))
+    b = subprocess.run([sys.executable, cli, "--model", str(only_config), "--random-weights", "--weights-seed", "3", "--kv-pages", "64",
+                        "--max-seq-len", "256", "--bench", "--bench-pp", "48", "--max-tokens", "8", "--bench-reps", "2", "--bench-batch", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert b.returncode == 0, b.stderr[-2000:]
+    assert "pp    96 tokens" in b.stderr and "tg    16 tokens" in b.stderr
+    no_rows = tmp_path / "cfg2"
+    no_rows.mkdir()
+    (no_rows / "config.json").write_text(json.dumps(cfg))
+    bad = subprocess.run([sys.executable, cli, "--model", str(no_rows), "--random-weights", "--prompt", "1"], capture_output=True, text=True,
+                         timeout=600)
+    assert bad.returncode != 0 and "only a checkpoint gives" in bad.stderr
