@@ -138,3 +138,34 @@ class KazedraConfig(ModelConfig):
     @property
     def num_hidden_layers(self) -> int:
         return len(self.raw["layers"])
+
+
+class KuzipelConfig(ModelConfig):
+    """Kuzipel (`"architecture": "Kuzipel"`): `vocab`, `width`, `norm.eps`, `residual_mult`, a list `layers`, each entry
+    with `type` ("latent_attention" or "wkv"), the mixer's sizes and constants under `mixer`, and `mlp`
+    (`{"kind": "moe", "expert": {"ff"}, "router": {"experts", "top"}, "shared": {"ff"} | null}` or null); optionally
+    `loop` (`{"start", "stop", "times"}`): layers start .. stop-1 run `times` times with the same weights."""
+
+    KNOWN_KEYS = ("architecture", "vocab", "width", "norm", "residual_mult", "layers", "loop", "torch_dtype", "dtype",
+                  "eos_token_id", "bos_token_id", "max_positions")
+
+    @property
+    def vocab_size(self) -> int:
+        return int(self.raw["vocab"])
+
+    @property
+    def hidden_size(self) -> int:
+        return int(self.raw["width"])
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.raw["layers"])
+
+    def run_order(self):
+        """Layer indices in the order they run (a repeated run of layers appears `times` times)."""
+        n = len(self.raw["layers"])
+        loop = self.raw.get("loop")
+        if not loop:
+            return list(range(n))
+        a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+        return list(range(a)) + list(range(a, b)) * times + list(range(b, n))

@@ -1,0 +1,315 @@
+// Matrix products over groups:  C_g[r, n] = sum_k A[row(r), a0(g) + k] * W_g[n, k],  one weight matrix per group.
+//
+// Two ways of saying which rows a group has:
+//   uniform    every group has the same M rows (grid.z = group): per-head products, where the head's slice of a
+//              row starts a_group_cols * g columns in and the result goes c_group_cols * g columns in;
+//   segmented  a list of rows sorted by group, seg[g] .. seg[g + 1] being group g's part of it (device memory, so a
+//              launch does not depend on the routing): routed experts.  Row r of the list reads A row a_rows[r]
+//              (null: r) and writes C row r.  The grid covers the most tiles any routing can make
+//              (rows / BM + groups); a CTA finds its group by walking seg, and leaves if there is no tile for it.
+// Optionally two weight matrices per group and the epilogue silu(A Wg^T) * (A Wu^T).
+//
+// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 32 tiles, four warps.  float32: FFMA with k
+// ascending for every output element, so a row's result does not depend on what else is in the batch.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int GG_BM = 64, GG_BN = 64;
+
+struct GroupedArgs {
+    const void* A;
+    int64_t lda;
+    const int* a_rows;
+    int64_t a_group_cols;
+    const void* W;
+    const void* W2;
+    int64_t w_group_stride, ldw;
+    void* C;
+    int64_t ldc, c_group_cols;
+    const int* seg;
+    int M, N, K, G;
+    int vec;   // rows of A and W start on 16 bytes and K is a multiple of 8 (bfloat16) / 4 (float32)
+};
+
+// Which group and which rows of the list this CTA has; false if it has none.
+__device__ __forceinline__ bool find_tile(const GroupedArgs& p, int& g, int& row0, int& row_end) {
+    if (!p.seg) {
+        g = blockIdx.z;
+        row0 = blockIdx.y * GG_BM;
+        row_end = p.M;
+        return row0 < row_end;
+    }
+    int t = blockIdx.y;
+    for (int e = 0; e < p.G; ++e) {
+        const int a = p.seg[e], b = p.seg[e + 1];
+        const int nt = (b - a + GG_BM - 1) / GG_BM;
+        if (t < nt) {
+            g = e;
+            row0 = a + t * GG_BM;
+            row_end = b;
+            return true;
+        }
+        t -= nt;
+    }
+    return false;
+}
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// --------------------------------------------------------------------------------------- bfloat16
+constexpr int GB_BK = 32, GB_LD = GB_BK + 8;   // padded rows: fragment loads hit 32 different banks
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// rows x 32 bfloat16 of `src` (row r at src_row(r), null rows zero) into a padded tile.
+template <typename RowFn>
+__device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], RowFn src_row, int k0, int K, int vec) {
+    const int tid = threadIdx.x;
+    if (vec) {
+        // 64 rows x 4 chunks of 8: two chunks a thread
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int idx = tid + e * 128, r = idx >> 2, c = (idx & 3) * 8;
+            const __nv_bfloat16* row = src_row(r);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row && k0 + c < K) v = *reinterpret_cast<const uint4*>(row + k0 + c);
+            *reinterpret_cast<uint4*>(&tile[r][c]) = v;
+        }
+    } else {
+        for (int idx = tid; idx < GG_BM * GB_BK; idx += 128) {
+            const int r = idx / GB_BK, c = idx % GB_BK;
+            const __nv_bfloat16* row = src_row(r);
+            tile[r][c] = (row && k0 + c < K) ? row[k0 + c] : __float2bfloat16_rn(0.f);
+        }
+    }
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArgs p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    int g, row0, row_end;
+    if (!find_tile(p, g, row0, row_end)) return;
+    __shared__ __align__(16) __nv_bfloat16 As[GG_BM][GB_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[GG_BN][GB_LD];
+    __shared__ __align__(16) __nv_bfloat16 Us[SWIGLU ? GG_BN : 1][GB_LD];
+    const int n0 = blockIdx.x * GG_BN;
+    const __nv_bfloat16* A = (const __nv_bfloat16*)p.A + p.a_group_cols * g;
+    const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + p.w_group_stride * g;
+    const __nv_bfloat16* U = SWIGLU ? (const __nv_bfloat16*)p.W2 + p.w_group_stride * g : nullptr;
+    auto a_row = [&](int r) -> const __nv_bfloat16* {
+        const int lr = row0 + r;
+        if (lr >= row_end) return nullptr;
+        return A + (int64_t)(p.a_rows ? p.a_rows[lr] : lr) * p.lda;
+    };
+    auto w_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? W + (int64_t)(n0 + r) * p.ldw : nullptr; };
+    auto u_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? U + (int64_t)(n0 + r) * p.ldw : nullptr; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    float acc[2][4][4], acu[SWIGLU ? 2 : 1][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[i][j][e] = 0.f;
+                if (SWIGLU) acu[i][j][e] = 0.f;
+            }
+
+    for (int k0 = 0; k0 < p.K; k0 += GB_BK) {
+        load_tile_bf16(As, a_row, k0, p.K, p.vec);
+        load_tile_bf16(Ws, w_row, k0, p.K, p.vec);
+        if (SWIGLU) load_tile_bf16(Us, u_row, k0, p.K, p.vec);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GB_BK; kk += 16) {
+            uint32_t a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm + i * 16 + gid;
+                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * tig]);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * tig]);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * tig + 8]);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * tig + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = wn + j * 8 + gid;
+                uint32_t b[2];
+                b[0] = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + 2 * tig]);
+                b[1] = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + 2 * tig + 8]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) mma_bf16(acc[i][j], a[i], b);
+                if (SWIGLU) {
+                    b[0] = *reinterpret_cast<const uint32_t*>(&Us[n][kk + 2 * tig]);
+                    b[1] = *reinterpret_cast<const uint32_t*>(&Us[n][kk + 2 * tig + 8]);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) mma_bf16(acu[i][j], a[i], b);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    __nv_bfloat16* C = (__nv_bfloat16*)p.C + p.c_group_cols * g;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int lr = row0 + wm + i * 16 + gid + half * 8;
+            if (lr >= row_end) continue;
+            __nv_bfloat16* crow = C + (int64_t)lr * p.ldc;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + wn + j * 8 + 2 * tig + e;
+                    if (n >= p.N) continue;
+                    float v = acc[i][j][half * 2 + e];
+                    if (SWIGLU) v = silu_f(v) * acu[i][j][half * 2 + e];   // the activation on the 32-bit sums
+                    crow[n] = __float2bfloat16_rn(v);
+                }
+        }
+}
+
+// ---------------------------------------------------------------------------------------- float32
+constexpr int GF_BK = 16;
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(256) grouped_gemm_f32_kernel(const GroupedArgs p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    int g, row0, row_end;
+    if (!find_tile(p, g, row0, row_end)) return;
+    __shared__ float As[GF_BK][GG_BM + 4];
+    __shared__ float Ws[GF_BK][GG_BN + 4];
+    __shared__ float Us[SWIGLU ? GF_BK : 1][GG_BN + 4];
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * GG_BN;
+    const float* A = (const float*)p.A + p.a_group_cols * g;
+    const float* W = (const float*)p.W + p.w_group_stride * g;
+    const float* U = SWIGLU ? (const float*)p.W2 + p.w_group_stride * g : nullptr;
+    const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+    float acc[4][4], acu[SWIGLU ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.f;
+            if (SWIGLU) acu[i][j] = 0.f;
+        }
+    // the A rows this thread loads, resolved once
+    int64_t a_off[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int r = (tid + e * 256) / GF_BK, lr = row0 + r;
+        a_off[e] = lr < row_end ? (int64_t)(p.a_rows ? p.a_rows[lr] : lr) * p.lda : -1;
+    }
+    for (int k0 = 0; k0 < p.K; k0 += GF_BK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = tid + e * 256;
+            const int r = idx / GF_BK, kk = idx % GF_BK;
+            const int gn = n0 + r, gk = k0 + kk;
+            As[kk][r] = (a_off[e] >= 0 && gk < p.K) ? A[a_off[e] + gk] : 0.f;
+            Ws[kk][r] = (gn < p.N && gk < p.K) ? W[(int64_t)gn * p.ldw + gk] : 0.f;
+            if (SWIGLU) Us[kk][r] = (gn < p.N && gk < p.K) ? U[(int64_t)gn * p.ldw + gk] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GF_BK; ++kk) {
+            float a[4], w[4], u[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][tm + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = Ws[kk][tn + j];
+                if (SWIGLU) u[j] = Us[kk][tn + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                    if (SWIGLU) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+    float* C = (float*)p.C + p.c_group_cols * g;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int lr = row0 + tm + i;
+        if (lr >= row_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tn + j;
+            if (gn < p.N) C[(int64_t)lr * p.ldc + gn] = SWIGLU ? silu_f(acc[i][j]) * acu[i][j] : acc[i][j];
+        }
+    }
+}
+
+}  // namespace
+
+// A: activations (dtype), rows lda apart.  W (and W2 with swiglu): [G][N, K], groups w_group_stride elements apart,
+// rows ldw apart.  C: rows ldc apart.  seg == null: uniform groups of M rows each; else the list has M rows in all.
+IMP_API int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const void* A, int64_t lda, int64_t a_group_cols,
+                             const int* a_rows, const void* W, const void* W2, int64_t w_group_stride, int64_t ldw, const int* seg,
+                             int M, int N, int K, int G, int swiglu, int dtype, void* stream) {
+    if (M == 0 || N == 0 || G == 0) return 0;
+    IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0 && G > 0, "imp_grouped_gemm: bad argument");
+    IMP_CHECK_ARG(!swiglu || W2, "imp_grouped_gemm: the gated epilogue needs a second weight");
+    GroupedArgs p;
+    p.A = A, p.lda = lda, p.a_rows = a_rows, p.a_group_cols = a_group_cols;
+    p.W = W, p.W2 = W2, p.w_group_stride = w_group_stride, p.ldw = ldw;
+    p.C = C, p.ldc = ldc, p.c_group_cols = c_group_cols, p.seg = seg;
+    p.M = M, p.N = N, p.K = K, p.G = G;
+    const int el = dtype == IMP_F32 ? 4 : 2, per16 = 16 / el;
+    auto aligned = [&](const void* q) { return q == nullptr || (uintptr_t)q % 16 == 0; };
+    p.vec = (K % per16 == 0 && lda % per16 == 0 && ldw % per16 == 0 && a_group_cols % per16 == 0 && w_group_stride % per16 == 0 &&
+             aligned(A) && aligned(W) && aligned(W2))
+                ? 1
+                : 0;
+    const int row_tiles = seg ? (M + GG_BM - 1) / GG_BM + G : (M + GG_BM - 1) / GG_BM;
+    IMP_CHECK_ARG(row_tiles <= 65535 && G <= 65535, "imp_grouped_gemm: too many row tiles or groups for one launch");
+    const dim3 grid((N + GG_BN - 1) / GG_BN, row_tiles, seg ? 1 : G);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == IMP_F32)
+        e = swiglu ? imp_launch(grouped_gemm_f32_kernel<true>, grid, dim3(256), 0, s, p) : imp_launch(grouped_gemm_f32_kernel<false>, grid, dim3(256), 0, s, p);
+    else
+        e = swiglu ? imp_launch(grouped_gemm_bf16_kernel<true>, grid, dim3(128), 0, s, p) : imp_launch(grouped_gemm_bf16_kernel<false>, grid, dim3(128), 0, s, p);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_grouped_gemm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// dst[g][c][r] = src[g][r][c]: per-group transposes of small weight matrices, at load time.
+template <typename T> __global__ void transpose_groups_kernel(T* __restrict__ dst, const T* __restrict__ src, int R, int Cn) {
+    const int64_t base = (int64_t)blockIdx.y * R * Cn;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < (int64_t)R * Cn; i += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / Cn), c = (int)(i % Cn);
+        dst[base + (int64_t)c * R + r] = src[base + i];
+    }
+}
+
+IMP_API int imp_transpose_groups(void* dst, const void* src, int G, int R, int Cn, int dtype, void* stream) {
+    if (G == 0 || R == 0 || Cn == 0) return 0;
+    IMP_CHECK_ARG(dst && src && G > 0 && R > 0 && Cn > 0 && G <= 65535, "imp_transpose_groups: bad argument");
+    const dim3 grid((unsigned)std::min<int64_t>(((int64_t)R * Cn + 255) / 256, 1024), G);
+    if (dtype == IMP_F32)
+        transpose_groups_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((float*)dst, (const float*)src, R, Cn);
+    else
+        transpose_groups_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)dst, (const __nv_bfloat16*)src, R, Cn);
+    IMP_RETURN_LAUNCH();
+}

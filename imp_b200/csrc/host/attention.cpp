@@ -382,7 +382,7 @@ void paged_attention(Step& st, Tensor out, const Tensor& q, const AttentionGeome
                      "paged_attention_generic_bias");
         return;
     }
-    if (rt.is_f32()) {
+    if (rt.is_f32() || g.dh % 16 || g.dh > 256) {   // float32, and head sizes the tensor-core libraries are not built for
         ++rt.launches;
         check_launch(imp_paged_attention_generic(out.data, out.stride0, q.data, q.stride0, c.k_pages, c.v_pages, c.block_table,
                                                  c.bt_stride, st.view.seq_of_token, st.view.positions, (int)rows(q), st.B(), g.hq,

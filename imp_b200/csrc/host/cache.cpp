@@ -56,7 +56,7 @@ int PagedGroup::pages_needed_n(int entries, int cur_len, int new_len) const {
 }
 
 size_t PagedGroup::layer_bytes(int elem) const {
-    return (size_t)2 * pool.size() * spec.num_kv_heads * page_size * spec.head_dim * (size_t)elem;
+    return (size_t)(spec.keys_only ? 1 : 2) * pool.size() * spec.num_kv_heads * page_size * spec.head_dim * (size_t)elem;
 }
 
 // ------------------------------------------------------------------------------------ manager
@@ -344,7 +344,7 @@ ImpCacheView CacheManager::layer_view(int position, int dtype) const {
         v.kind = 1;
         const size_t lb = g.layer_bytes((int)elem_size(dtype));
         v.k_pages = g.storage.data() ? (char*)g.storage.data() + (size_t)ref.index * lb : nullptr;
-        v.v_pages = g.storage.data() ? (char*)v.k_pages + lb / 2 : nullptr;
+        v.v_pages = g.storage.data() ? (char*)v.k_pages + (g.spec.keys_only ? 0 : lb / 2) : nullptr;
         v.num_pages = g.pool.size();
         v.kv_heads = g.spec.num_kv_heads;
         v.page_size = g.page_size;

@@ -61,7 +61,7 @@ struct PagedGroup {
     int width = 0;                      // columns of the table
     std::vector<int32_t> table;         // [slots, width]
     std::vector<int> n_entries;         // logical pages per slot (held or given back)
-    DeviceBuffer storage;               // [layers, 2, pages, kv_heads, page_size, head_dim]
+    DeviceBuffer storage;               // [layers, 2 (1 with keys_only), pages, kv_heads, page_size, head_dim]
     PagedGroup(int gid, const CacheSpec& spec, int page_size, int num_pages, int num_slots, int width);
     int32_t* row(int slot) { return table.data() + (size_t)slot * width; }
     const int32_t* row(int slot) const { return table.data() + (size_t)slot * width; }

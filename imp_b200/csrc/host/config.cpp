@@ -402,6 +402,221 @@ ModelPlan kazedra_plan(const KazedraConfig& cfg) {
     return plan;
 }
 
+// ------------------------------------------------------------------------------------ Kuzipel
+KuzipelConfig KuzipelConfig::from_json(const Json& d, const std::string& where) {
+    KuzipelConfig c;
+    c.architecture = d.get_string("architecture", "Kuzipel");
+    c.vocab_size = positive("vocab", require_int(d, "vocab", where), where);
+    c.hidden_size = positive("width", require_int(d, "width", where), where);
+    c.max_position_embeddings = positive("max_positions", d.get_int("max_positions", 1 << 16), where);
+    c.torch_dtype = d.get_string("torch_dtype", d.get_string("dtype", "bfloat16"));
+    if (c.torch_dtype != "bfloat16" && c.torch_dtype != "float32")
+        bad(where + ": torch_dtype '" + c.torch_dtype + "' is not supported (bfloat16 or float32)");
+    if (const Json* eos = d.find("eos_token_id")) {
+        if (eos->is_array()) {
+            for (const auto& e : eos->items())
+                if (e.is_int()) c.eos_token_ids.push_back((int)e.as_int());
+        } else if (eos->is_int()) {
+            c.eos_token_ids.push_back((int)eos->as_int());
+        }
+    }
+    c.bos_token_id = d.get_int("bos_token_id", -1);
+    c.raw = d;
+    c.norm_eps = require_float(require_object(d, "norm", where), "eps", where + ": norm");
+    if (!(c.norm_eps > 0)) bad(where + ": norm.eps must be positive");
+    c.residual_mult = d.get_double("residual_mult", 1.0);
+    const Json& layers = require(d, "layers", where);
+    if (!layers.is_array() || layers.size() == 0) bad(where + ": 'layers' must be a non-empty list");
+    int i = 0;
+    for (const Json& lj : layers.items()) {
+        const std::string lw = where + ": layers[" + std::to_string(i++) + "]";
+        if (!lj.is_object()) bad(lw + " must be an object");
+        Layer l;
+        l.type = lj.get_string("type", "");
+        const Json& m = require_object(lj, "mixer", lw);
+        const std::string mw = lw + ".mixer";
+        l.heads = positive("heads", require_int(m, "heads", mw), mw);
+        l.dim = positive("dim", require_int(m, "dim", mw), mw);
+        if (l.type == "latent_attention") {
+            l.rot_dim = positive("rot_dim", require_int(m, "rot_dim", mw), mw);
+            l.vdim = positive("vdim", require_int(m, "vdim", mw), mw);
+            l.kv_rank = positive("kv_rank", require_int(m, "kv_rank", mw), mw);
+            l.q_rank = positive("q_rank", require_int(m, "q_rank", mw), mw);
+            l.scale = require_float(m, "scale", mw);
+            const Json& rot = require_object(m, "rot", mw);
+            l.rot_base = require_float(rot, "base", mw + ".rot");
+            l.rot_dims = positive("dims", rot.get_int("dims", l.rot_dim), mw + ".rot");
+            if (!(l.rot_base > 0)) bad(mw + ".rot: base must be positive");
+            if (l.rot_dims % 2 || l.rot_dims > l.rot_dim)
+                bad(mw + ".rot: dims " + std::to_string(l.rot_dims) + " must be even and at most rot_dim " + std::to_string(l.rot_dim));
+        } else if (l.type == "wkv") {
+            l.decay_rank = m.get_int("decay_rank", 0);
+            if (l.decay_rank < 0) bad(mw + ": decay_rank must not be negative");
+        } else {
+            bad(lw + ": unknown layer type '" + l.type + "' (known: latent_attention, wkv)");
+        }
+        if (const Json* f = lj.find("mlp")) {
+            if (f->is_object()) {
+                const std::string fw = lw + ".mlp", kind = f->get_string("kind", "");
+                if (kind != "moe") bad(fw + ": unknown kind '" + kind + "' (known: moe)");
+                l.has_mlp = true;
+                l.expert_ff = positive("ff", require_int(require_object(*f, "expert", fw), "ff", fw + ".expert"), fw + ".expert");
+                const Json& r = require_object(*f, "router", fw);
+                l.experts = positive("experts", require_int(r, "experts", fw + ".router"), fw + ".router");
+                l.top = positive("top", require_int(r, "top", fw + ".router"), fw + ".router");
+                if (l.top > l.experts) bad(fw + ".router: top " + std::to_string(l.top) + " exceeds the " + std::to_string(l.experts) + " experts");
+                if (const Json* s = f->find("shared")) {
+                    if (s->is_object()) l.shared_ff = positive("ff", require_int(*s, "ff", fw + ".shared"), fw + ".shared");
+                    else if (!s->is_null()) bad(fw + ".shared must be an object or null");
+                }
+            } else if (!f->is_null()) {
+                bad(lw + ".mlp must be an object or null");
+            }
+        }
+        c.layers.push_back(l);
+    }
+    c.num_hidden_layers = (int64_t)c.layers.size();
+    if (const Json* lp = d.find("loop")) {
+        if (lp->is_object()) {
+            c.has_loop = true;
+            c.loop_start = require_int(*lp, "start", where + ": loop");
+            c.loop_stop = require_int(*lp, "stop", where + ": loop");
+            c.loop_times = positive("times", require_int(*lp, "times", where + ": loop"), where + ": loop");
+            if (c.loop_start < 0 || c.loop_stop <= c.loop_start || c.loop_stop > c.num_hidden_layers)
+                bad(where + ": loop: 0 <= start < stop <= " + std::to_string(c.num_hidden_layers) + " is required, got " +
+                    std::to_string(c.loop_start) + " and " + std::to_string(c.loop_stop));
+        } else if (!lp->is_null()) {
+            bad(where + ": 'loop' must be an object or null");
+        }
+    }
+    return c;
+}
+
+Json KuzipelConfig::to_json() const {
+    Json j = raw.is_object() ? raw : Json::object();
+    j["architecture"] = architecture;
+    j["vocab"] = vocab_size;
+    j["width"] = hidden_size;
+    j["torch_dtype"] = torch_dtype;
+    j.erase("dtype");
+    return j;
+}
+
+std::vector<int> KuzipelConfig::run_order() const {
+    std::vector<int> o;
+    const int L = (int)layers.size();
+    if (!has_loop) {
+        for (int i = 0; i < L; ++i) o.push_back(i);
+        return o;
+    }
+    for (int i = 0; i < (int)loop_start; ++i) o.push_back(i);
+    for (int64_t pass = 0; pass < loop_times; ++pass) {
+        o.push_back(L);
+        for (int i = (int)loop_start; i < (int)loop_stop; ++i) o.push_back(i);
+    }
+    for (int i = (int)loop_stop; i < L; ++i) o.push_back(i);
+    return o;
+}
+
+// Layer i's tensors are 'l<i>.norm1', 'l<i>.mix.*', 'l<i>.norm2', 'l<i>.mlp.*', 'l<i>.ls1', 'l<i>.ls2'; the map before
+// every pass of a repeated run is 'loop.in'.  A layer that runs several times gets a cache per run.
+ModelPlan kuzipel_plan(const KuzipelConfig& cfg) {
+    const int64_t d = cfg.hidden_size;
+    ModelPlan plan;
+    plan.architecture = cfg.architecture;
+    plan.hidden_size = d;
+    plan.vocab_size = cfg.vocab_size;
+    plan.max_positions = cfg.max_position_embeddings;
+    auto norm = [&](const std::string& tensor) {
+        PartSpec n;
+        n.kind = "layernorm";
+        n.params["size"] = d;
+        n.params["eps"] = cfg.norm_eps;
+        n.tensors = {{"weight", tensor}};
+        return n;
+    };
+    for (size_t i = 0; i < cfg.layers.size(); ++i) {
+        const KuzipelConfig::Layer& l = cfg.layers[i];
+        const std::string p = "l" + std::to_string(i) + ".", a = p + "mix.", f = p + "mlp.";
+        PartSpec mixer;
+        mixer.params["hidden_size"] = d;
+        mixer.params["num_heads"] = l.heads;
+        mixer.params["head_dim"] = l.dim;
+        mixer.params["norm_eps"] = cfg.norm_eps;
+        if (l.type == "latent_attention") {
+            mixer.kind = "latent_attention";
+            mixer.params["rot_dim"] = l.rot_dim;
+            mixer.params["value_dim"] = l.vdim;
+            mixer.params["kv_rank"] = l.kv_rank;
+            mixer.params["q_rank"] = l.q_rank;
+            mixer.params["scale"] = l.scale;
+            mixer.params["rot_base"] = l.rot_base;
+            mixer.params["rot_dims"] = l.rot_dims;
+            mixer.params["max_positions"] = cfg.max_position_embeddings;
+            mixer.tensors = {{"q_down", a + "dq"}, {"q_norm", a + "dq.norm"}, {"q_up", a + "uq"}, {"kv_down", a + "dkv"},
+                             {"kv_norm", a + "dkv.norm"}, {"k_up", a + "uk"}, {"v_up", a + "uv"}, {"o_proj", a + "o"}};
+        } else {
+            mixer.kind = "wkv";
+            mixer.params["decay_rank"] = l.decay_rank;
+            mixer.tensors = {{"mu_r", a + "mu.r"}, {"mu_k", a + "mu.k"}, {"mu_v", a + "mu.v"}, {"mu_g", a + "mu.g"}, {"mu_w", a + "mu.w"},
+                             {"r_proj", a + "r"}, {"k_proj", a + "k"}, {"v_proj", a + "v"}, {"g_proj", a + "g"}, {"decay_down", a + "w1"},
+                             {"decay_up", a + "w2"}, {"decay_bias", a + "w0"}, {"bonus", a + "u"}, {"out_norm", a + "norm"}, {"o_proj", a + "o"}};
+        }
+        LayerSpec layer;
+        layer.block = "scaled_prenorm";
+        layer.block_params["hidden_size"] = d;
+        layer.block_params["residual_mult"] = cfg.residual_mult;
+        layer.block_params["has_ffn"] = l.has_mlp;
+        layer.block_tensors = {{"mixer_scale", p + "ls1"}};
+        layer.parts = {{"mixer_norm", norm(p + "norm1")}, {"mixer", mixer}};
+        if (l.has_mlp) {
+            PartSpec ffn;
+            ffn.kind = "routed_experts";
+            ffn.params["hidden_size"] = d;
+            ffn.params["num_experts"] = l.experts;
+            ffn.params["top_k"] = l.top;
+            ffn.params["expert_size"] = l.expert_ff;
+            ffn.params["shared_size"] = l.shared_ff;
+            ffn.tensors = {{"router", f + "router"}, {"router_bias", f + "router.b"}};
+            for (int64_t e = 0; e < l.experts; ++e) {
+                const std::string n = std::to_string(e), t = f + "e" + n + ".";
+                ffn.tensors.emplace_back("gate_" + n, t + "gate");
+                ffn.tensors.emplace_back("up_" + n, t + "up");
+                ffn.tensors.emplace_back("down_" + n, t + "down");
+            }
+            if (l.shared_ff > 0) {
+                ffn.tensors.emplace_back("shared_gate", f + "shared.gate");
+                ffn.tensors.emplace_back("shared_up", f + "shared.up");
+                ffn.tensors.emplace_back("shared_down", f + "shared.down");
+                ffn.tensors.emplace_back("shared_mix", f + "shared.sg");
+            }
+            layer.block_tensors.emplace_back("ffn_scale", p + "ls2");
+            layer.parts.emplace_back("ffn_norm", norm(p + "norm2"));
+            layer.parts.emplace_back("feed_forward", ffn);
+        }
+        plan.layers.push_back(layer);
+    }
+    if (cfg.has_loop) {
+        LayerSpec inject;
+        inject.block = "stream_reinject";
+        inject.block_params["hidden_size"] = d;
+        inject.block_tensors = {{"weight", "loop.in"}};
+        plan.layers.push_back(inject);
+        plan.has_order = true;
+        plan.order = cfg.run_order();
+    }
+    plan.embedding.kind = "token_embedding";
+    plan.embedding.params["vocab_size"] = cfg.vocab_size;
+    plan.embedding.params["hidden_size"] = d;
+    plan.embedding.tensors = {{"weight", "embed"}};
+    plan.final_norm = norm("final.norm");
+    plan.head.kind = "linear_head";
+    plan.head.params["vocab_size"] = cfg.vocab_size;
+    plan.head.params["hidden_size"] = d;
+    plan.head.tensors = {{"weight", "head"}};
+    return plan;
+}
+
 // ------------------------------------------------------------------------------------ registry
 namespace {
 std::mutex g_arch_mutex;
@@ -426,6 +641,13 @@ void ensure_builtin_archs() {
         };
         k.plan = [](const Json& d) { return kazedra_plan(KazedraConfig::from_json(d, "config.json")); };
         archs()[k.name] = k;
+        Architecture z;
+        z.name = "Kuzipel";
+        z.parse_config = [](const Json& d, const std::string& where) -> std::shared_ptr<ModelConfig> {
+            return std::make_shared<KuzipelConfig>(KuzipelConfig::from_json(d, where));
+        };
+        z.plan = [](const Json& d) { return kuzipel_plan(KuzipelConfig::from_json(d, "config.json")); };
+        archs()[z.name] = z;
     });
 }
 }  // namespace

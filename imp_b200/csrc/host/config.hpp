@@ -86,6 +86,35 @@ struct KazedraConfig : ModelConfig {
 // gives; an optional model-wide `bias_buckets` key fixes them (random weights need it).
 ModelPlan kazedra_plan(const KazedraConfig& cfg);
 
+// Kuzipel ("architecture": "Kuzipel"): a pre-norm decoder with layer norms (weight, no bias), one mixer per layer
+// (latent attention or the wkv recurrence), routed experts with a shared expert as feed-forward (or none), a learned
+// factor per channel and one constant on every branch, and optionally a run of layers that is repeated with the same
+// weights, the stream being re-made from itself and the embedding's output before every pass.  config.json lists
+// the layers one by one; the keys are this family's own.
+struct KuzipelConfig : ModelConfig {
+    struct Layer {
+        std::string type;                       // "latent_attention" | "wkv"
+        int64_t heads = 0, dim = 0;             // both mixers
+        int64_t rot_dim = 0, vdim = 0, kv_rank = 0, q_rank = 0, rot_dims = 0;   // latent attention
+        double scale = 0, rot_base = 10000.0;
+        int64_t decay_rank = 0;                 // wkv: 0 = the checkpoint's tensor decides
+        bool has_mlp = false;
+        int64_t experts = 0, top = 0, expert_ff = 0, shared_ff = 0;   // shared_ff 0 = no shared expert
+    };
+    std::vector<Layer> layers;
+    double norm_eps = 1e-5, residual_mult = 1.0;
+    bool has_loop = false;
+    int64_t loop_start = 0, loop_stop = 0, loop_times = 1;
+
+    static KuzipelConfig from_json(const Json& d, const std::string& where);
+    Json to_json() const override;
+    // Layer indices in the order they run: those before the repeated run once, the run `times` times, the rest once.
+    // With a repeated run, the index num_hidden_layers stands for the map that re-makes the stream before every pass.
+    std::vector<int> run_order() const;
+};
+
+ModelPlan kuzipel_plan(const KuzipelConfig& cfg);
+
 // ------------------------------------------------------------------------------------ registry
 struct Architecture {
     std::string name;

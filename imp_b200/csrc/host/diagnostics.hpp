@@ -6,6 +6,9 @@
 //   IMP_B200_DEBUG_FORWARD=1  per-stage min / max / mean / L2 / count of non-finite values and the ten
 //                             largest logits, with a stream synchronisation at every stage
 //                             (src/graph/executor_forward.cu:168-246).
+//   IMP_B200_DUMP_STREAM=DIR  the residual stream after every layer run of every step (what the layer left pending
+//                             added in), as DIR/step<n>_run<j>.f32: float32 [tokens, hidden].  For comparing a model
+//                             layer by layer with another implementation; synchronises at every layer.
 #pragma once
 
 #include <string>
@@ -19,6 +22,8 @@ struct Diagnostics {
     Diagnostics();
     ~Diagnostics();
     const bool profile, debug;
+    const std::string dump_dir;
+    void dump_stream(Step& st, int run, const Tensor& h, const Branch& pending);
     void begin(Step& st);
     void stage(Step& st, const std::string& name, const Tensor& t);
     void end(Step& st, const Tensor& logits);
@@ -32,7 +37,7 @@ private:
     std::vector<cudaEvent_t> events_;
     std::vector<std::string> names_, sum_names_;
     std::vector<double> sums_;
-    int n_stamps_ = 0, steps_ = 0;
+    int n_stamps_ = 0, steps_ = 0, dump_step_ = -1;
     double total_ms_ = 0;
     DeviceBuffer stats_;
 };

@@ -105,6 +105,44 @@ int imp_typical_filter(float* logits, int64_t ld, int n_rows, int V, const float
                        void* stream);
 int imp_sample_mirostat(const float* logits, int64_t ld, int n_rows, int V, const int* active, const float* temperature,
                         const float* mu, const float* uniform, int* out, float* surprise, void* stream);
+
+// layer norm with the residual sum, and streams whose branches carry a factor per column (layernorm.cu)
+int imp_add_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows,
+                      int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream);
+int imp_scale_columns(void* x, int64_t stride, int n_rows, int n_cols, const float* s, int dtype, void* stream);
+int imp_concat_streams(void* out, const float* h, const void* branch, const float* col_scale, const float* x0, int n_rows,
+                       int d, int act_dtype, void* stream);
+// products over groups: per-head matrices, routed experts (grouped_gemm.cu)
+int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const void* A, int64_t lda, int64_t a_group_cols,
+                     const int* a_rows, const void* W, const void* W2, int64_t w_group_stride, int64_t ldw, const int* seg,
+                     int M, int N, int K, int G, int swiglu, int dtype, void* stream);
+int imp_transpose_groups(void* dst, const void* src, int G, int R, int Cn, int dtype, void* stream);
+// latent attention (latent_attention.cu)
+int imp_latent_prepare(const void* proj, int64_t ld, int n_tokens, int q_rank, int kv_rank, int rot, const float* wq,
+                       const float* wkv, float eps, void* cq, int64_t cq_ld, const float* cos_tab, const float* sin_tab,
+                       int rot_dims, int max_pos, const int* positions, const int* seq_of_token, const int* block_table,
+                       int bt_stride, int n_seqs, void* pages, int page_size, int num_pages, int act_dtype, int* status,
+                       void* stream);
+int imp_latent_query_rope(const void* q, int64_t q_ld, int n_tokens, int H, int D, int rot, void* out, int64_t out_ld, int kv_rank,
+                          const float* cos_tab, const float* sin_tab, int rot_dims, int max_pos, const int* positions,
+                          int act_dtype, int* status, void* stream);
+// the wkv recurrence (wkv.cu)
+int imp_wkv_max_head_dim(void);
+int imp_wkv_mix(const void* x, int64_t ldx, const float* mu, float* prev_state, const int* seq_of_token, const int* q_start,
+                const int* slots, int n_tokens, int n_seqs, int d, void* out, int update_state, int act_dtype, int* status,
+                void* stream);
+int imp_tanh_inplace(void* x, int64_t n, int dtype, void* stream);
+int imp_wkv_scan(const void* r, const void* k, const void* v, int64_t ld, const float* dlog, const float* w0, const float* u,
+                 float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, int act_dtype,
+                 void* stream);
+int imp_wkv_output(void* y, const float* o, const void* g, int64_t ldg, const float* w, float eps, int n_tokens, int H, int D,
+                   int act_dtype, void* stream);
+// routed experts (moe.cu)
+int imp_moe_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
+                  int* idx, float* wts, float* gate, int act_dtype, void* stream);
+int imp_moe_sort(const int* idx, int n_tokens, int top, int E, int* seg, int* row_token, int* pair_row, void* stream);
+int imp_moe_combine(void* out, const void* y, const int* pair_row, const float* wts, int n_tokens, int top, const void* shared,
+                    const float* gate, int d, int act_dtype, void* stream);
 }
 
 // Epilogues of the tcgen05 products.

@@ -151,11 +151,16 @@ static bool gemm_tc_swap_partials(Runtime& rt, Tensor out, const Tensor& a, cons
 }
 
 Tensor summed(Runtime& rt, const Branch& b) {
-    if (!b.split()) return b.t;
-    const int epi = b.t.dtype == F32 ? TC_OUT_F32 : TC_OUT_BF16;
-    ++rt.launches;
-    check_launch(imp_gemm_bf16_tc_swap_sum(b.t.data, b.t.stride0, epi, b.parts, (int)rows(b.t), (int)cols(b.t), b.n_splits, rt.stream),
-                 "gemm_bf16_tc_swap_sum");
+    if (b.split()) {
+        const int epi = b.t.dtype == F32 ? TC_OUT_F32 : TC_OUT_BF16;
+        ++rt.launches;
+        check_launch(imp_gemm_bf16_tc_swap_sum(b.t.data, b.t.stride0, epi, b.parts, (int)rows(b.t), (int)cols(b.t), b.n_splits, rt.stream),
+                     "gemm_bf16_tc_swap_sum");
+    }
+    if (b.col_scale && !b.empty()) {
+        ++rt.launches;
+        check_launch(imp_scale_columns(b.t.data, b.t.stride0, (int)rows(b.t), (int)cols(b.t), b.col_scale, b.t.dtype, rt.stream), "scale_columns");
+    }
     return b.t;
 }
 
@@ -250,7 +255,9 @@ void add_rmsnorm(Runtime& rt, Tensor h, const Branch& branch, const Tensor& weig
     need(rows_idx ? n_out == n_rows : n_out == rows(h), "add_rmsnorm: out has the wrong number of rows");
     const int write_h = rows_idx ? 0 : 1;
     const void* plain = nullptr;
-    if (branch.split()) {
+    if (branch.col_scale) {
+        plain = summed(rt, branch).data;     // this norm adds plain tensors: the factor per column is applied first
+    } else if (branch.split()) {
         need(rows(branch.t) == rows(h) && cols(branch.t) == d && branch.t.dtype == out.dtype, "add_rmsnorm: branch shape or type");
         const int rc = imp_add_rmsnorm_split((float*)h.data, branch.parts, rows(h) * (int64_t)d, branch.n_splits, weight.data, out.data,
                                              rows_idx, n_out, d, eps, offset, out.dtype, weight.dtype, write_h, rt.stream);

@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstring>
 
 #include "diagnostics.hpp"
 #include "kernels.h"
@@ -72,7 +73,38 @@ Json HostModel::tensor_info(int compute_dtype) const {
 }
 
 // ---------------------------------------------------------------------------------- diagnostics
-Diagnostics::Diagnostics() : profile(env_flag("IMP_B200_PROFILE", false)), debug(env_flag("IMP_B200_DEBUG_FORWARD", false)) {}
+Diagnostics::Diagnostics()
+    : profile(env_flag("IMP_B200_PROFILE", false)), debug(env_flag("IMP_B200_DEBUG_FORWARD", false)), dump_dir(env_string("IMP_B200_DUMP_STREAM", "")) {}
+
+void Diagnostics::dump_stream(Step& st, int run, const Tensor& h, const Branch& pending) {
+    if (run == 0) ++dump_step_;
+    const size_t n = (size_t)numel(h), d = (size_t)cols(h);
+    std::vector<float> hs(n);
+    IMP_CUDA(cudaMemcpyAsync(hs.data(), h.data, n * 4, cudaMemcpyDeviceToHost, st.rt->stream));
+    IMP_CUDA(cudaStreamSynchronize(st.rt->stream));
+    if (!pending.empty() && !pending.split()) {
+        std::vector<char> raw(n * elem_size(pending.t.dtype));
+        std::vector<float> scale(d, 1.f);
+        IMP_CUDA(cudaMemcpyAsync(raw.data(), pending.t.data, raw.size(), cudaMemcpyDeviceToHost, st.rt->stream));
+        if (pending.col_scale) IMP_CUDA(cudaMemcpyAsync(scale.data(), pending.col_scale, d * 4, cudaMemcpyDeviceToHost, st.rt->stream));
+        IMP_CUDA(cudaStreamSynchronize(st.rt->stream));
+        for (size_t i = 0; i < n; ++i) {
+            float v;
+            if (pending.t.dtype == F32) {
+                v = ((const float*)raw.data())[i];
+            } else {
+                const uint32_t bits = (uint32_t)((const uint16_t*)raw.data())[i] << 16;
+                memcpy(&v, &bits, 4);
+            }
+            hs[i] += scale[i % d] * v;
+        }
+    }
+    const std::string path = dump_dir + "/step" + std::to_string(dump_step_) + "_run" + std::to_string(run) + ".f32";
+    if (FILE* f = fopen(path.c_str(), "wb")) {
+        fwrite(hs.data(), 4, n, f);
+        fclose(f);
+    }
+}
 Diagnostics::~Diagnostics() {
     for (auto e : events_) cudaEventDestroy(e);
 }
@@ -258,7 +290,8 @@ void DeviceModel::build(const std::vector<std::pair<std::string, Tensor>>& place
         PartSpec bs;
         bs.kind = layer.block;
         bs.params = layer.block_params;
-        blocks_.push_back(part_cast<Block>(factory_.build("block", bs, {}, parts), "a block"));
+        bs.tensors = layer.block_tensors;
+        blocks_.push_back(part_cast<Block>(factory_.build("block", bs, take(bs), parts), "a block"));
     }
     final_norm_ = part_cast<Norm>(factory_.build("norm", plan_.final_norm, take(plan_.final_norm)), "a norm");
     head_ = part_cast<Head>(factory_.build("head", plan_.head, take(plan_.head)), "a head");
@@ -275,6 +308,16 @@ void DeviceModel::finish_build() {
         after_ok[(size_t)order_[j]] = after_ok[(size_t)order_[j]] && next_takes;
     }
     for (size_t i = 0; i < blocks_.size(); ++i) blocks_[i]->defer_pending = after_ok[i];
+    // The same for a pending branch that carries a factor per column.
+    std::vector<bool> scale_ok(blocks_.size(), true);
+    for (size_t j = 0; j < order_.size(); ++j) {
+        const bool next_takes = j + 1 < order_.size() ? blocks_[(size_t)order_[j + 1]]->takes_column_scale() : final_norm_->takes_column_scale();
+        scale_ok[(size_t)order_[j]] = scale_ok[(size_t)order_[j]] && next_takes;
+    }
+    for (size_t i = 0; i < blocks_.size(); ++i) {
+        blocks_[i]->scale_pending = scale_ok[i];
+        keep_embedding_ = keep_embedding_ || blocks_[i]->wants_embedding();
+    }
     // Cache needs: one entry per mixer of every run position (one entry, possibly empty, for a position with a
     // single mixer or none, so that models of one-mixer layers number their caches by run position), and which
     // entry each position's first mixer uses.
@@ -331,7 +374,7 @@ void DeviceModel::finish_build() {
         }
     }
     diag_ = std::make_unique<Diagnostics>();
-    if (!diag_->profile && !diag_->debug) diag_.reset();
+    if (!diag_->profile && !diag_->debug && diag_->dump_dir.empty()) diag_.reset();
 }
 
 void DeviceModel::attach_cache(CacheManager* cache) {
@@ -365,6 +408,12 @@ Tensor DeviceModel::forward(Step& st) {
     if (diag_) diag_->begin(st);
     Tensor h = embedding_->forward(st);
     stage(st, "embedding", h);
+    st.embedding_out = Tensor{};
+    if (keep_embedding_) {
+        // the stream is rewritten in place from here on; a block that reads the embedding's output gets a copy
+        st.embedding_out = rt_->empty(rows(h), cols(h), h.dtype, /*step=*/true);
+        IMP_CUDA(cudaMemcpyAsync(st.embedding_out.data, h.data, (size_t)numel(h) * elem_size(h.dtype), cudaMemcpyDeviceToDevice, rt_->stream));
+    }
     Branch pending;
     for (size_t j = 0; j < order_.size(); ++j) {
         rt_->arena->next_layer();
@@ -373,6 +422,7 @@ Tensor DeviceModel::forward(Step& st) {
         LayerCache* lc = &layer_caches_[(size_t)cache_first_[j]];
         if (cache_count_[j] == 1 && !lc->view.kind) lc = nullptr;
         pending = blocks_[(size_t)order_[j]]->forward(st, h, pending, lc);
+        if (diag_ && !diag_->dump_dir.empty()) diag_->dump_stream(st, (int)j, h, pending);
     }
     st.layer = -1;
     Tensor logits{};

@@ -88,7 +88,7 @@ private:
     std::vector<CacheSpec> cache_specs_;
     std::vector<LayerCache> layer_caches_;
     std::vector<TilingSpec> tilings_;
-    bool graph_safe_ = true;
+    bool graph_safe_ = true, keep_embedding_ = false;
     CacheManager* cache_ = nullptr;
     std::unique_ptr<Diagnostics> diag_;
 };

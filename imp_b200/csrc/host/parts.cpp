@@ -14,7 +14,7 @@ const char* const PART_CATEGORIES[7] = {"mixer", "feed_forward", "norm", "positi
 std::string CacheSpec::key() const {
     if (kind == None) return "none";
     if (kind == Paged)
-        return "paged:" + std::to_string(num_kv_heads) + "x" + std::to_string(head_dim) + "w" + std::to_string(window);
+        return "paged:" + std::to_string(num_kv_heads) + "x" + std::to_string(head_dim) + "w" + std::to_string(window) + (keys_only ? "k" : "");
     std::string k = "state";
     for (const auto& s : states) {
         k += ":" + s.name + "/" + dtype_name(s.dtype);
@@ -31,6 +31,7 @@ Json CacheSpec::to_json() const {
         j["num_kv_heads"] = num_kv_heads;
         j["head_dim"] = head_dim;
         j["window"] = window;
+        if (keys_only) j["keys_only"] = true;
     } else {
         j["kind"] = "state";
         Json ts = Json::array();
@@ -55,6 +56,7 @@ CacheSpec CacheSpec::from_json(const Json& j) {
         s.num_kv_heads = (int)j.at("num_kv_heads").as_int();
         s.head_dim = (int)j.at("head_dim").as_int();
         s.window = (int)j.get_int("window", 0);
+        s.keys_only = j.get_bool("keys_only", false);
         if (s.num_kv_heads <= 0 || s.head_dim <= 0 || s.window < 0)
             fail(IMP_ERROR_INVALID_ARG, "cache spec: kv heads and head size must be positive, the window not negative");
     } else if (kind == "state") {
@@ -243,10 +245,12 @@ void FeedForward::call(Step& st, ImpCall& c) {
 void Block::call(Step& st, ImpCall& c) {
     LayerCache lc;
     if (c.cache) lc.view = *c.cache;
-    const bool keep = defer_pending;
+    const bool keep = defer_pending, keep_scale = scale_pending;
     defer_pending = false;
+    scale_pending = false;
     Branch b = forward(st, c.h, branch_of(c.branch), c.cache ? &lc : nullptr);
     defer_pending = keep;
+    scale_pending = keep_scale;
     c.has_out = b.empty() ? 0 : 1;
     if (!b.empty()) copy_out(st, summed(st, b), c.out);
 }

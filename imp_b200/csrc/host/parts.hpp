@@ -48,6 +48,7 @@ struct StateTensorSpec {
 struct CacheSpec {
     enum Kind { None = 0, Paged = 1, State = 2 } kind = None;
     int num_kv_heads = 0, head_dim = 0, window = 0;
+    bool keys_only = false;       // paged: one vector per token and kv head; the value pages are the key pages
     std::vector<StateTensorSpec> states;
     std::string key() const;      // equal keys share a cache group
     Json to_json() const;
@@ -86,6 +87,7 @@ struct Step {
     std::vector<Tiles> tiles;                  // per tiling the model declared (empty in decode-only steps)
     struct Diagnostics* diag = nullptr;        // stage timers / statistics when a debugging switch is set
     int layer = -1;                            // index of the layer that is running (for stage names)
+    Tensor embedding_out{};                    // a copy of the embedding's output, kept when a block asks for it (Block::wants_embedding)
     int context = 0;                           // the sequences' mean length after this step, rounded to a power of two: what
                                                // launch choices may depend on (a decode graph is kept per batch size and context)
     int T() const { return view.n_tokens; }
@@ -108,11 +110,14 @@ struct Branch;
 void stage(Step& st, const char* name, const Branch& b);   // an unsummed branch stops the timer and has no statistics
 
 // A branch output: nothing, a tensor, or the unsummed parts of one ([n_splits, M, N] float32 whose
-// sum in split order, rounded to `t`'s type, is the value that belongs into `t`).
+// sum in split order, rounded to `t`'s type, is the value that belongs into `t`).  With `col_scale` the
+// branch stands for that tensor times a 32-bit factor per column: whoever adds it into the stream multiplies in
+// 32-bit while adding (a norm that says takes_column_scale()), and summed() applies it for everyone else.
 struct Branch {
     Tensor t{};
     float* parts = nullptr;
     int n_splits = 0;
+    const float* col_scale = nullptr;   // float32 [cols], or null
     bool empty() const { return t.data == nullptr; }
     bool split() const { return parts != nullptr; }
     static Branch of(const Tensor& t) { Branch b; b.t = t; return b; }
@@ -130,6 +135,7 @@ struct Part {
 struct Norm : Part {
     const char* category() const override { return "norm"; }
     virtual bool takes_split_sum() const { return false; }
+    virtual bool takes_column_scale() const { return false; }   // multiplies a branch's col_scale in while adding
     virtual Tensor add_norm(Step& st, Tensor h, const Branch& branch, const int32_t* rows = nullptr, int n_rows = 0) = 0;
     void call(Step& st, ImpCall& c) override;
 };
@@ -165,6 +171,9 @@ struct Block : Part {
     const char* category() const override { return "block"; }
     bool defer_pending = false;                          // set by the model: the pending it returns may be unsummed
     virtual bool takes_split_sum() const { return false; }   // the pending it is given may be unsummed
+    bool scale_pending = false;                          // set by the model: the pending it returns may carry a col_scale
+    virtual bool takes_column_scale() const { return false; }   // the pending it is given may carry a col_scale
+    virtual bool wants_embedding() const { return false; }      // reads Step::embedding_out
     virtual Mixer* mixer() const { return nullptr; }     // the part that owns this layer's cache, if any
     // A block with several mixers names them in the order of its mixer slots; each owns a cache, and forward()
     // gets them as an array in that order.
@@ -237,6 +246,7 @@ const PartClass& part_class(const std::string& category, const std::string& kind
 std::vector<std::string> known_parts(const std::string& category);
 void ensure_builtin_parts();   // registers the library's own kinds once
 void register_mixer_parts();    // parts_mixers.cpp: the kinds beyond plain attention (called by ensure_builtin_parts)
+void register_routed_parts();   // parts_routed.cpp: layer norm, latent attention, wkv, routed experts, blocks with scaled branches
 
 // Builds parts and owns them.  Parts without tensors are shared between equal specs.
 class PartFactory {

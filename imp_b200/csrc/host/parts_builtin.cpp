@@ -352,6 +352,7 @@ void ensure_builtin_parts() {
         register_part_class("embedding", "token_embedding", simple_class<TokenEmbedding>(&TokenEmbedding::specs), true);
         register_part_class("head", "linear_head", simple_class<LinearHead>(&LinearHead::specs), true);
         register_mixer_parts();
+        register_routed_parts();
     });
 }
 

@@ -117,6 +117,11 @@ Json ModelPlan::to_json() const {
         Json ps = Json::object();
         for (const auto& kv : l.parts) ps[kv.first] = kv.second.to_json();
         lj["parts"] = ps;
+        if (!l.block_tensors.empty()) {
+            Json bt = Json::object();
+            for (const auto& kv : l.block_tensors) bt[kv.first] = kv.second;
+            lj["block_tensors"] = bt;
+        }
         lj["cache_from"] = l.cache_from < 0 ? Json() : Json(l.cache_from);
         ls.push(lj);
     }
@@ -150,6 +155,13 @@ ModelPlan ModelPlan::from_json(const Json& j) {
             if (!ps.is_object()) fail(IMP_ERROR_INVALID_MODEL, "plan: " + where + ".parts must be an object");
             for (const auto& m : ps.members())
                 l.parts.emplace_back(m.first, PartSpec::from_json(m.second, where + ".parts." + m.first));
+            if (const Json* bt = lj.find("block_tensors"))
+                if (bt->is_object())
+                    for (const auto& m : bt->members()) {
+                        if (!m.second.is_string())
+                            fail(IMP_ERROR_INVALID_MODEL, "plan: " + where + ".block_tensors." + m.first + " must be a tensor name");
+                        l.block_tensors.emplace_back(m.first, m.second.as_string());
+                    }
             const Json* cf = lj.find("cache_from");
             l.cache_from = (cf && !cf->is_null()) ? (int)cf->as_int() : -1;
             p.layers.push_back(std::move(l));
@@ -203,6 +215,16 @@ std::vector<std::pair<std::string, TensorSpec>> ModelPlan::expected_tensors() co
         const PartClass& bc = part_class("block", l.block);
         if (!bc.part_slots) fail(IMP_ERROR_INVALID_MODEL, "block kind '" + l.block + "' declares no part slots");
         const auto slots = bc.part_slots(l.block_params);
+        if (bc.tensor_specs) {
+            // a block may hold tensors of its own (per-channel scales of its branches, a map over the stream)
+            PartSpec own;
+            own.kind = l.block;
+            own.params = l.block_params;
+            own.tensors = l.block_tensors;
+            collect(out, "block", own);
+        } else if (!l.block_tensors.empty()) {
+            fail(IMP_ERROR_INVALID_MODEL, "plan error: layer " + std::to_string(li) + ": block '" + l.block + "' takes no tensors of its own");
+        }
         for (const auto& s : slots) {
             const PartSpec* ps = l.part(s.name);
             if (!ps)

@@ -47,6 +47,7 @@ struct LayerSpec {
     std::string block = "prenorm";
     Json block_params = Json::object();
     std::vector<std::pair<std::string, PartSpec>> parts;   // slot name -> part
+    std::vector<std::pair<std::string, std::string>> block_tensors;   // tensors of the block itself: local name -> checkpoint name
     int cache_from = -1;   // index of the layer whose cache this layer's mixer reads (it writes none)
     const PartSpec* part(const std::string& slot) const;
     PartSpec* part(const std::string& slot);

@@ -1,0 +1,166 @@
+// Layer norm with a weight and no bias, fused with the residual sum, and the small kernels that go
+// with a stream whose branches carry a factor per column.
+//
+//   h += s (.) branch            (s: 32-bit factor per column, optional; branch optional)
+//   y  = (h - mean(h)) / sqrt(var(h) + eps) * w,   var = mean((h - mean)^2)
+//
+// The residual stream is 32-bit; mean, variance and the scaling are 32-bit.  One block per row with a
+// fixed block size; the row is held in registers between the passes (up to LN_MAX_PER_THREAD values a
+// thread, the rest re-read), so the order of every sum depends on the width alone.
+#include "common.cuh"
+
+constexpr int LN_BLOCK = 256;
+constexpr int LN_KEEP = 16;   // values a thread keeps in registers: rows up to 4096 wide are read once
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(LN_BLOCK) add_layernorm_kernel(float* __restrict__ h, const TA* __restrict__ branch,
+                                                                 const float* __restrict__ col_scale, const TW* __restrict__ w,
+                                                                 TA* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+                                                                 int write_h) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int64_t src = rows ? rows[r] : r;
+    float* hrow = h + src * d;
+    const TA* brow = branch ? branch + src * d : nullptr;
+    float keep[LN_KEEP];
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < LN_KEEP; ++e) {
+        const int i = threadIdx.x + e * LN_BLOCK;
+        float v = 0.f;
+        if (i < d) {
+            v = hrow[i];
+            if (brow) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
+            if (write_h && brow) hrow[i] = v;
+        }
+        keep[e] = v;
+        sum += v;
+    }
+    for (int i = threadIdx.x + LN_KEEP * LN_BLOCK; i < d; i += LN_BLOCK) {
+        float v = hrow[i];
+        if (brow) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
+        if (write_h && brow) hrow[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < LN_KEEP; ++e) {
+        const int i = threadIdx.x + e * LN_BLOCK;
+        if (i < d) {
+            const float c = keep[e] - mean;
+            ss = fmaf(c, c, ss);
+        }
+    }
+    const bool stored = write_h && brow;   // beyond the kept part the row is read again: from h if it was stored, else recomputed
+    for (int i = threadIdx.x + LN_KEEP * LN_BLOCK; i < d; i += LN_BLOCK) {
+        float v = hrow[i];
+        if (brow && !stored) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
+        const float c = v - mean;
+        ss = fmaf(c, c, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+    TA* orow = out + (int64_t)r * d;
+#pragma unroll
+    for (int e = 0; e < LN_KEEP; ++e) {
+        const int i = threadIdx.x + e * LN_BLOCK;
+        if (i < d) orow[i] = from_float<TA>((keep[e] - mean) * inv * to_float(w[i]));
+    }
+    for (int i = threadIdx.x + LN_KEEP * LN_BLOCK; i < d; i += LN_BLOCK) {
+        float v = hrow[i];
+        if (brow && !stored) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
+        orow[i] = from_float<TA>((v - mean) * inv * to_float(w[i]));
+    }
+}
+
+// h: [*, d] float32 stream; branch (optional, dense [*, d] of the activation type) is added first, times col_scale
+// (optional float32 [d]).  rows: optional gather list (then h is left as it is: write_h must be 0).
+IMP_API int imp_add_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows,
+                              int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream) {
+    if (n_out_rows == 0) return 0;
+    IMP_CHECK_ARG(h && w && out && d > 0 && n_out_rows > 0, "imp_add_layernorm: bad argument");
+    IMP_CHECK_ARG(!(rows && write_h), "imp_add_layernorm: a gather list and write_h exclude each other");
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_out_rows), block(LN_BLOCK);
+    cudaError_t e;
+    if (act_dtype == IMP_F32) {
+        if (w_dtype == IMP_F32)
+            e = imp_launch(add_layernorm_kernel<float, float>, grid, block, 0, s, h, (const float*)branch, col_scale, (const float*)w,
+                           (float*)out, rows, d, eps, write_h);
+        else
+            e = imp_launch(add_layernorm_kernel<float, __nv_bfloat16>, grid, block, 0, s, h, (const float*)branch, col_scale,
+                           (const __nv_bfloat16*)w, (float*)out, rows, d, eps, write_h);
+    } else {
+        if (w_dtype == IMP_F32)
+            e = imp_launch(add_layernorm_kernel<__nv_bfloat16, float>, grid, block, 0, s, h, (const __nv_bfloat16*)branch, col_scale,
+                           (const float*)w, (__nv_bfloat16*)out, rows, d, eps, write_h);
+        else
+            e = imp_launch(add_layernorm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, h, (const __nv_bfloat16*)branch,
+                           col_scale, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, d, eps, write_h);
+    }
+    if (e != cudaSuccess) {
+        imp_set_error("imp_add_layernorm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// x[r][c] *= s[c], the product made in 32-bit.
+template <typename TA> __global__ void scale_columns_kernel(TA* __restrict__ x, int64_t stride, int n_cols, const float* __restrict__ s) {
+    pdl_wait();
+    pdl_launch_dependents();
+    TA* row = x + (int64_t)blockIdx.x * stride;
+    for (int i = threadIdx.x; i < n_cols; i += blockDim.x) row[i] = from_float<TA>(to_float(row[i]) * s[i]);
+}
+
+IMP_API int imp_scale_columns(void* x, int64_t stride, int n_rows, int n_cols, const float* s, int dtype, void* stream) {
+    if (n_rows == 0 || n_cols == 0) return 0;
+    IMP_CHECK_ARG(x && s && n_rows > 0 && n_cols > 0, "imp_scale_columns: bad argument");
+    cudaError_t e = dtype == IMP_F32
+                        ? imp_launch(scale_columns_kernel<float>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (float*)x, stride, n_cols, s)
+                        : imp_launch(scale_columns_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream,
+                                     (__nv_bfloat16*)x, stride, n_cols, s);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_scale_columns: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// out[r] = [ h[r] + s (.) branch[r] ; x0[r] ] rounded to the activation type: the input of a map over the stream and
+// a second stream side by side.  The sum is not stored: whoever runs the map overwrites h with its result.
+template <typename TA>
+__global__ void concat_streams_kernel(TA* __restrict__ out, const float* __restrict__ h, const TA* __restrict__ branch,
+                                      const float* __restrict__ col_scale, const float* __restrict__ x0, int d) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t r = blockIdx.x;
+    const float* hrow = h + r * d;
+    const float* xrow = x0 + r * d;
+    const TA* brow = branch ? branch + r * d : nullptr;
+    TA* orow = out + r * 2 * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = hrow[i];
+        if (brow) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
+        orow[i] = from_float<TA>(v);
+        orow[d + i] = from_float<TA>(xrow[i]);
+    }
+}
+
+IMP_API int imp_concat_streams(void* out, const float* h, const void* branch, const float* col_scale, const float* x0, int n_rows,
+                               int d, int act_dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(out && h && x0 && n_rows > 0 && d > 0, "imp_concat_streams: bad argument");
+    cudaError_t e = act_dtype == IMP_F32
+                        ? imp_launch(concat_streams_kernel<float>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (float*)out, h,
+                                     (const float*)branch, col_scale, x0, d)
+                        : imp_launch(concat_streams_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream,
+                                     (__nv_bfloat16*)out, h, (const __nv_bfloat16*)branch, col_scale, x0, d);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_concat_streams: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}

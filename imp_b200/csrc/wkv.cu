@@ -1,0 +1,256 @@
+// The wkv mixer's own kernels: a linear recurrence with a matrix state per head and inputs mixed with the
+// previous token's.
+//
+//   mix_s[t] = x[t] + (x[t-1] - x[t]) * mu_s            s = r, k, v, g, w;  x[-1] is the state's `prev` (zero at a
+//                                                        request's start)
+//   w[t]     = exp(-exp(d[t] + w0))                      d: the decay's low-rank product, 32-bit
+//   o[t]     = (S + diag(u) k[t] v[t]^T)^T r[t]          per head, S [D keys, D values] in 32-bit
+//   S        = diag(w[t]) S + k[t] v[t]^T
+//   y[t]     = o[t] / sqrt(mean(o[t]^2) + eps) * g_norm * gate[t]     per head
+//
+// Everything but the projections is 32-bit.  The scan gives a (sequence, head) to one CTA; a column of S (one value
+// channel) is spread over four lanes, each with every fourth key row in registers, so a token costs D/4
+// multiply-adds a lane for the read-out, as many for the update, and two shuffles.  Inputs come in chunks of
+// 16 tokens through shared memory.  The order of every sum depends on D alone: a token's result is the same bits
+// however the prompt is cut and whatever else is in the batch.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------ token shift
+// out: [5][T, d] of the activation type (r, k, v, g, w).  update_state (steps of single tokens): the token's row
+// becomes the state's `prev` in the same pass; otherwise wkv_shift_state_kernel does that afterwards.
+template <typename TA>
+__global__ void wkv_mix_kernel(const TA* __restrict__ x, int64_t ldx, const float* __restrict__ mu /* [5, d] */, float* __restrict__ prev_state,
+                               const int* __restrict__ seq_of_token, const int* __restrict__ q_start, const int* __restrict__ slots, int n_tokens,
+                               int n_seqs, int d, TA* __restrict__ out, int update_state, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    if (seq < 0 || seq >= n_seqs) {
+        if (threadIdx.x == 0) imp_report(status, IMP_BAD_SEQUENCE);
+        return;
+    }
+    const bool first = t == q_start[seq];
+    float* prev = prev_state + (int64_t)slots[seq] * d;
+    const TA* cur = x + (int64_t)t * ldx;
+    const TA* before = first ? nullptr : x + (int64_t)(t - 1) * ldx;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float c = to_float(cur[i]);
+        const float p = before ? to_float(before[i]) : prev[i];
+        const float diff = p - c;
+#pragma unroll
+        for (int s = 0; s < 5; ++s) out[((int64_t)s * n_tokens + t) * d + i] = from_float<TA>(fmaf(diff, mu[s * d + i], c));
+        if (update_state) prev[i] = c;
+    }
+}
+
+template <typename TA>
+__global__ void wkv_shift_state_kernel(const TA* __restrict__ x, int64_t ldx, float* __restrict__ prev_state, const int* __restrict__ q_start,
+                                       const int* __restrict__ slots, int d) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x;
+    const int end = q_start[seq + 1];
+    if (end <= q_start[seq]) return;
+    const TA* last = x + (int64_t)(end - 1) * ldx;
+    float* prev = prev_state + (int64_t)slots[seq] * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) prev[i] = to_float(last[i]);
+}
+
+template <typename TA> __global__ void tanh_kernel(TA* __restrict__ x, int64_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] = from_float<TA>(tanhf(to_float(x[i])));
+}
+
+// ------------------------------------------------------------------------------------------------- scan
+constexpr int WKV_LANES = 4;
+
+template <typename TA, int RPT>
+__global__ void __launch_bounds__(RPT * 16) wkv_scan_kernel(const TA* __restrict__ r, const TA* __restrict__ k, const TA* __restrict__ v,
+                                                             int64_t ld, const float* __restrict__ dlog, const float* __restrict__ w0,
+                                                             const float* __restrict__ u, float* __restrict__ state, float* __restrict__ out,
+                                                             const int* __restrict__ q_start, const int* __restrict__ slots, int H, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int DP = RPT * WKV_LANES;   // D rounded up to the rows the lanes hold
+    constexpr int WKV_CHUNK = RPT > 32 ? 8 : 16;   // five arrays of WKV_CHUNK x DP floats stay under 48 KB
+    __shared__ float s_r[WKV_CHUNK][DP], s_k[WKV_CHUNK][DP], s_w[WKV_CHUNK][DP], s_b[WKV_CHUNK][DP], s_v[WKV_CHUNK][DP];
+    const int h = blockIdx.x, seq = blockIdx.y;
+    const int t0 = q_start[seq], t1 = q_start[seq + 1];
+    if (t1 <= t0) return;
+    const int tid = threadIdx.x, j = tid / WKV_LANES, sub = tid % WKV_LANES;
+    const bool col = j < D;
+    float* S = state + ((int64_t)slots[seq] * H + h) * D * D;
+    float s[RPT];
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+        const int i = sub + WKV_LANES * ii;
+        s[ii] = (col && i < D) ? S[(int64_t)i * D + j] : 0.f;
+    }
+    const int64_t hoff = (int64_t)h * D;
+    for (int c0 = t0; c0 < t1; c0 += WKV_CHUNK) {
+        const int n = min(WKV_CHUNK, t1 - c0);
+        __syncthreads();   // the chunk before has been read
+        for (int e = tid; e < n * DP; e += blockDim.x) {
+            const int tt = e / DP, i = e % DP;
+            float rv = 0.f, kv = 0.f, wv = 1.f, vv = 0.f, bv = 0.f;
+            if (i < D) {
+                const int64_t at = (int64_t)(c0 + tt) * ld + hoff + i;
+                rv = to_float(r[at]);
+                kv = to_float(k[at]);
+                vv = to_float(v[at]);
+                wv = expf(-expf(dlog[(int64_t)(c0 + tt) * H * D + hoff + i] + w0[hoff + i]));
+                bv = rv * u[hoff + i] * kv;
+            }
+            s_r[tt][i] = rv, s_k[tt][i] = kv, s_w[tt][i] = wv, s_v[tt][i] = vv, s_b[tt][i] = bv;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = col ? s_v[tt][j] : 0.f;
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < RPT; ++ii) {
+                const int i = sub + WKV_LANES * ii;
+                a = fmaf(s_r[tt][i], s[ii], a);
+                b += s_b[tt][i];
+            }
+            float o = fmaf(vj, b, a);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+            for (int ii = 0; ii < RPT; ++ii) {
+                const int i = sub + WKV_LANES * ii;
+                s[ii] = fmaf(s_w[tt][i], s[ii], s_k[tt][i] * vj);
+            }
+            if (col && sub == 0) out[(int64_t)(c0 + tt) * H * D + hoff + j] = o;
+        }
+    }
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+        const int i = sub + WKV_LANES * ii;
+        if (col && i < D) S[(int64_t)i * D + j] = s[ii];
+    }
+}
+
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(g): one warp per (token, head).
+template <typename TA>
+__global__ void wkv_output_kernel(TA* __restrict__ y, const float* __restrict__ o, const TA* __restrict__ g, int64_t ldg,
+                                  const float* __restrict__ w, float eps, int n_tokens, int H, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_tokens * H) return;
+    const int64_t t = item / H;
+    const int h = (int)(item % H);
+    const float* orow = o + (t * H + h) * D;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) ss = fmaf(orow[i], orow[i], ss);
+    const float inv = rsqrtf(warp_sum(ss) / (float)D + eps);
+    for (int i = lane; i < D; i += 32) {
+        const float z = to_float(g[t * ldg + (int64_t)h * D + i]);
+        y[(t * H + h) * D + i] = from_float<TA>(orow[i] * inv * w[h * D + i] * (z / (1.f + expf(-z))));
+    }
+}
+
+template <typename TA, int RPT>
+cudaError_t launch_scan(const void* r, const void* k, const void* v, int64_t ld, const float* dlog, const float* w0, const float* u,
+                        float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, cudaStream_t s) {
+    // an ordinary dependent: its CTAs hold many registers and would sit on the SMs while the kernels before it run
+    wkv_scan_kernel<TA, RPT><<<dim3(H, n_seqs), RPT * 16, 0, s>>>((const TA*)r, (const TA*)k, (const TA*)v, ld, dlog, w0, u, state, out, q_start, slots, H, D);
+    return cudaGetLastError();
+}
+
+template <typename TA>
+cudaError_t scan_by_size(const void* r, const void* k, const void* v, int64_t ld, const float* dlog, const float* w0, const float* u,
+                         float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, cudaStream_t s) {
+    const int rpt = (D + WKV_LANES - 1) / WKV_LANES;
+    if (rpt <= 8) return launch_scan<TA, 8>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s);
+    if (rpt <= 16) return launch_scan<TA, 16>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s);
+    if (rpt <= 24) return launch_scan<TA, 24>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s);
+    if (rpt <= 32) return launch_scan<TA, 32>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s);
+    return launch_scan<TA, 64>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s);
+}
+
+}  // namespace
+
+IMP_API int imp_wkv_max_head_dim() { return 64 * WKV_LANES; }
+
+IMP_API int imp_wkv_mix(const void* x, int64_t ldx, const float* mu, float* prev_state, const int* seq_of_token, const int* q_start,
+                        const int* slots, int n_tokens, int n_seqs, int d, void* out, int update_state, int act_dtype, int* status,
+                        void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(x && mu && prev_state && seq_of_token && q_start && slots && out && d > 0, "imp_wkv_mix: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = act_dtype == IMP_F32
+                        ? imp_launch(wkv_mix_kernel<float>, dim3(n_tokens), dim3(256), 0, s, (const float*)x, ldx, mu, prev_state, seq_of_token,
+                                     q_start, slots, n_tokens, n_seqs, d, (float*)out, update_state, status)
+                        : imp_launch(wkv_mix_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx, mu, prev_state,
+                                     seq_of_token, q_start, slots, n_tokens, n_seqs, d, (__nv_bfloat16*)out, update_state, status);
+    if (e == cudaSuccess && !update_state)
+        e = act_dtype == IMP_F32
+                ? imp_launch(wkv_shift_state_kernel<float>, dim3(n_seqs), dim3(256), 0, s, (const float*)x, ldx, prev_state, q_start, slots, d)
+                : imp_launch(wkv_shift_state_kernel<__nv_bfloat16>, dim3(n_seqs), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx, prev_state,
+                             q_start, slots, d);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_wkv_mix: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+IMP_API int imp_tanh_inplace(void* x, int64_t n, int dtype, void* stream) {
+    if (n == 0) return 0;
+    IMP_CHECK_ARG(x && n > 0, "imp_tanh_inplace: bad argument");
+    const dim3 grid((unsigned)std::min<int64_t>((n + 255) / 256, 4096));
+    cudaError_t e = dtype == IMP_F32 ? imp_launch(tanh_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, (float*)x, n)
+                                     : imp_launch(tanh_kernel<__nv_bfloat16>, grid, dim3(256), 0, (cudaStream_t)stream, (__nv_bfloat16*)x, n);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_tanh_inplace: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// r, k, v: [T, H*D] of the activation type, rows ld apart (three tensors with one stride); dlog: float32 [T, H*D]
+// dense; w0: [H*D]; u: [H, D]; state: [slots, H, D, D]; out: float32 [T, H*D] dense.
+IMP_API int imp_wkv_scan(const void* r, const void* k, const void* v, int64_t ld, const float* dlog, const float* w0, const float* u,
+                         float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, int act_dtype,
+                         void* stream) {
+    if (n_seqs == 0) return 0;
+    IMP_CHECK_ARG(r && k && v && dlog && w0 && u && state && out && q_start && slots && H > 0 && D > 0, "imp_wkv_scan: bad argument");
+    IMP_CHECK_ARG(D <= imp_wkv_max_head_dim(), "imp_wkv_scan: head size %d above %d", D, imp_wkv_max_head_dim());
+    IMP_CHECK_ARG(n_seqs <= 65535, "imp_wkv_scan: too many sequences");
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = act_dtype == IMP_F32 ? scan_by_size<float>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s)
+                                         : scan_by_size<__nv_bfloat16>(r, k, v, ld, dlog, w0, u, state, out, q_start, slots, n_seqs, H, D, s);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_wkv_scan: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+IMP_API int imp_wkv_output(void* y, const float* o, const void* g, int64_t ldg, const float* w, float eps, int n_tokens, int H, int D,
+                           int act_dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(y && o && g && w && H > 0 && D > 0, "imp_wkv_output: bad argument");
+    const int warps = 8;
+    const dim3 grid((unsigned)(((int64_t)n_tokens * H + warps - 1) / warps));
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = act_dtype == IMP_F32 ? imp_launch(wkv_output_kernel<float>, grid, dim3(warps * 32), 0, s, (float*)y, o, (const float*)g, ldg,
+                                                      w, eps, n_tokens, H, D)
+                                         : imp_launch(wkv_output_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, s, (__nv_bfloat16*)y, o,
+                                                      (const __nv_bfloat16*)g, ldg, w, eps, n_tokens, H, D);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_wkv_output: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
