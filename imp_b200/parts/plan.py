@@ -38,11 +38,14 @@ class LayerSpec:
     """One layer: a block kind (`block`, `block_params`) and the parts in the slots that block declares
     (`parts`: slot name -> PartSpec).  The usual slots (mixer, feed_forward, mixer_norm, ffn_norm) can be
     named as keyword arguments and attributes.  `cache_from`: index of the layer whose cache this layer's
-    mixer reads (it writes none)."""
+    mixer reads (it writes none).  `block_tensors`: tensors of the block itself (local name -> checkpoint name),
+    for block kinds that hold some (factors per channel of their branches, a map over the stream)."""
 
     def __init__(self, block: str = "prenorm", parts: Optional[Dict[str, PartSpec]] = None,
-                 block_params: Optional[Dict[str, Any]] = None, cache_from: Optional[int] = None, **slots: PartSpec):
+                 block_params: Optional[Dict[str, Any]] = None, cache_from: Optional[int] = None,
+                 block_tensors: Optional[Dict[str, str]] = None, **slots: PartSpec):
         self.block = block
+        self.block_tensors = dict(block_tensors or {})
         self.parts = dict(parts or {})
         self.parts.update(slots)
         self.block_params = dict(block_params or {})
@@ -55,19 +58,22 @@ class LayerSpec:
         raise AttributeError(name)
 
     def __setattr__(self, name: str, value) -> None:
-        if name in ("block", "parts", "block_params", "cache_from"):
+        if name in ("block", "parts", "block_params", "cache_from", "block_tensors"):
             object.__setattr__(self, name, value)
         else:
             self.parts[name] = value
 
     def to_json(self) -> Dict[str, Any]:
-        return {"block": self.block, "block_params": self.block_params,
-                "parts": {k: v.to_json() for k, v in self.parts.items()}, "cache_from": self.cache_from}
+        j = {"block": self.block, "block_params": self.block_params,
+             "parts": {k: v.to_json() for k, v in self.parts.items()}, "cache_from": self.cache_from}
+        if self.block_tensors:
+            j["block_tensors"] = dict(self.block_tensors)
+        return j
 
     @classmethod
     def from_json(cls, j: Dict[str, Any]) -> "LayerSpec":
         return cls(j.get("block", "prenorm"), {k: PartSpec.from_json(v) for k, v in j["parts"].items()},
-                   j.get("block_params") or {}, j.get("cache_from"))
+                   j.get("block_params") or {}, j.get("cache_from"), j.get("block_tensors") or {})
 
 
 @dataclass

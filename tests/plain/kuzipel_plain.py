@@ -130,10 +130,21 @@ def route(h, W, pre, top):
     return idx, torch.softmax(val, dim=-1)
 
 
-def moe(h, W, pre, c):
+def route_margin(h, W, pre, top):
+    """Per token, how far the last chosen logit lies above the first refused one (infinite when every expert is chosen)."""
+    z = h @ W[pre + "router"].T + W[pre + "router.b"]
+    if top >= z.shape[-1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    val = torch.topk(z, top + 1, dim=-1).values
+    return val[:, top - 1] - val[:, top]
+
+
+def moe(h, W, pre, c, margins=None):
     T = h.shape[0]
     out = torch.zeros(T, W[pre + "e0.down"].shape[0], dtype=h.dtype)
     idx, wt = route(h, W, pre, c["router"]["top"])
+    if margins is not None:
+        margins.append(route_margin(h, W, pre, c["router"]["top"]))
     for t in range(T):
         for j in range(idx.shape[1]):
             e = int(idx[t, j])
@@ -160,8 +171,9 @@ def run_order(cfg):
     return order, starts
 
 
-def forward(tokens, W, cfg, streams=None):
-    """tokens [T] -> logits [T, vocab].  With `streams` (a list), the residual stream after every layer run is appended."""
+def forward(tokens, W, cfg, streams=None, margins=None):
+    """tokens [T] -> logits [T, vocab].  With `streams` (a list), the residual stream after every layer run is appended;
+    with `margins` (a list), every router's margin per token (see route_margin)."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x0 = W["embed"][torch.as_tensor(tokens)]
     x = x0
@@ -179,7 +191,7 @@ def forward(tokens, W, cfg, streams=None):
             raise ValueError(layer["type"])
         x = x + m * W[pre + "ls1"] * y
         if layer.get("mlp"):
-            x = x + m * W[pre + "ls2"] * moe(layer_norm(x, W[pre + "norm2"], eps), W, pre + "mlp.", layer["mlp"])
+            x = x + m * W[pre + "ls2"] * moe(layer_norm(x, W[pre + "norm2"], eps), W, pre + "mlp.", layer["mlp"], margins)
         if streams is not None:
             streams.append(x.clone())
     return layer_norm(x, W["final.norm"], eps) @ W["head"].T
