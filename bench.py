@@ -27,6 +27,7 @@ Other runs, each printing its own JSON line:
     IMP_B200_NVCC_FLAGS=-DIMP_TIMELINE python bench.py --only timeline [--batch B] [--context C] [--workload 0.6b|14b]   (a table, not JSON)
     python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
     python bench.py --arch kazedra [--layers N] [--batch B]    Kazedra beside Qwen3 at equal sizes: prefill and decode
+    python bench.py --arch kuzipel [--layers N] [--batch B]    Kuzipel beside Kazedra and Qwen3 at equal sizes
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
 """
@@ -717,9 +718,27 @@ def kazedra_config(width, heads, kv_heads, ff, layers, vocab):
             "layers": [lay] * layers, "max_positions": 8192}
 
 
+def kuzipel_config(width, heads, kv_heads, ff, layers, vocab):
+    """Layers alternate between the wkv recurrence (heads of 64) and latent attention (heads of 128 + 64 rotated entries at
+    width 4096, 64 + 32 at width 1024; a cached vector of 256 resp. 128 numbers per token); routed experts whose two chosen
+    experts and shared expert together have the inner size of the dense feed-forward beside them."""
+    wide = width >= 2048
+    latent = {"heads": heads, "dim": 128 if wide else 64, "rot_dim": 64 if wide else 32, "vdim": 128 if wide else 64,
+              "kv_rank": 192 if wide else 96, "q_rank": width // 4, "scale": (192 if wide else 96) ** -0.5,
+              "rot": {"base": 10000.0, "dims": 64 if wide else 32}}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "top": 2}, "shared": {"ff": ff // 3}}
+    lays = [{"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "mlp": mlp} if i % 2 == 0 else
+            {"type": "latent_attention", "mixer": latent, "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Kuzipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 1.0, "layers": lays,
+            "max_positions": 8192}
+
+
 def run_arch(args):
-    """Prefill and decode of Kazedra beside the Qwen3 decoder at equal sizes (random weights): a 2,048-token prompt whole
-    and in 512-token portions, and decode steps of `--batch` sequences at context 2,048, device time between CUDA events."""
+    """Prefill and decode of Kazedra or Kuzipel beside the models the engine already had at equal sizes (random weights): a
+    2,048-token prompt whole and in 512-token portions, and decode steps of `--batch` sequences at context 2,048, device
+    time between CUDA events."""
+    if args.arch == "kuzipel":
+        return run_arch_kuzipel(args)
     peaks, peak_src = read_peaks()
     layers, vocab, B = args.layers or 4, 32768, args.batch
     if args.only in ("prefill", "decode"):
@@ -774,6 +793,61 @@ def run_arch(args):
     return 0
 
 
+def run_arch_kuzipel(args):
+    peaks, peak_src = read_peaks()
+    layers, vocab, B = args.layers or 4, 32768, args.batch
+    if args.only in ("prefill", "decode"):
+        width, heads, kv, ff = ARCH_SHAPES[args.shape]
+        rng = random.Random(0)
+        eng, _ = make_engine(kuzipel_config(width, heads, kv, ff, layers, vocab), args, B, 4096)
+        if args.only == "prefill":
+            ms = time_prefill(eng, rng, vocab, args.tokens or 2048, args.chunk, reps=max(1, args.steps))
+            print(json.dumps({"arch": "kuzipel", "only": "prefill", "shape": args.shape, "layers": layers, "tokens": args.tokens or 2048,
+                              "chunk": args.chunk, "ms": spread(ms)}))
+        else:
+            reqs = start_decoding(eng, rng, vocab, B, args.context or 2048, args.steps + args.warmup + 16)
+            for _ in range(args.warmup):
+                eng.step()
+            ms = timed_steps(eng, args.steps, B) / args.steps
+            print(json.dumps({"arch": "kuzipel", "only": "decode", "shape": args.shape, "layers": layers, "batch": B,
+                              "context": args.context or 2048, "ms_per_step": round(ms, 4)}))
+            stop(eng, reqs)
+        return 0
+    out = {"arch": "kuzipel", "beside": ["kazedra", "qwen3"], "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
+    with ClockSampler() as clocks:
+        for name, (width, heads, kv, ff) in ARCH_SHAPES.items():
+            models = {"kuzipel": kuzipel_config(width, heads, kv, ff, layers, vocab),
+                      "kazedra": kazedra_config(width, heads, kv, ff, layers, vocab),
+                      "qwen3": dict(MODEL, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
+                                    intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)}
+            row = {}
+            for label, cfgd in models.items():
+                rng = random.Random(0)
+                eng, _ = make_engine(cfgd, args, B, 4096)
+                whole = time_prefill(eng, rng, vocab, 2048, 0, reps=5)
+                cut = time_prefill(eng, rng, vocab, 2048, 512, reps=5)
+                reqs = start_decoding(eng, rng, vocab, B, 2048, args.steps + args.warmup + 16)
+                for _ in range(args.warmup):
+                    eng.step()
+                before = eng.info()
+                ms = timed_steps(eng, args.steps, B) / args.steps
+                info = eng.info()
+                stop(eng, reqs)
+                row[label] = {"prefill_2048_ms": spread(whole), "prefill_tok_s": round(2048e3 / statistics.median(whole)),
+                              "prefill_512_portions_ms": spread(cut), "decode_ms_per_step": round(ms, 4),
+                              "decode_tok_s": round(B * 1e3 / ms), "weight_bytes": info["model"]["weight_bytes"],
+                              "launches_per_decode_step": (info["launches"] - before["launches"]) / args.steps,
+                              "graph_replays": info["graph_replays"] - before["graph_replays"], "fallback_calls": info["fallback_calls"]}
+                del eng
+            for other in ("kazedra", "qwen3"):
+                row["prefill_ratio_to_" + other] = round(row["kuzipel"]["prefill_2048_ms"]["median"] / row[other]["prefill_2048_ms"]["median"], 3)
+                row["decode_ratio_to_" + other] = round(row["kuzipel"]["decode_ms_per_step"] / row[other]["decode_ms_per_step"], 3)
+            out["shapes"][name] = row
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args):
     """The one offline install the contract describes is attempted once (it cannot succeed: the reference is a
     CMake C++/CUDA project without setup.py or pyproject.toml, it needs CUDA >= 13.1 where this image has 12.9,
@@ -806,7 +880,7 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "mixed"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
-    ap.add_argument("--arch", default="", choices=["", "kazedra"],
+    ap.add_argument("--arch", default="", choices=["", "kazedra", "kuzipel"],
                     help="prefill and decode of this architecture beside the Qwen3 decoder at equal sizes (not the default workload)")
     ap.add_argument("--shape", default="8b", choices=["1b", "8b"], help="with --arch and --only: which of the shapes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")

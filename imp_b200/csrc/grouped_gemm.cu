@@ -9,7 +9,7 @@
 //              (rows / BM + groups); a CTA finds its group by walking seg, and leaves if there is no tile for it.
 // Optionally two weight matrices per group and the epilogue silu(A Wg^T) * (A Wu^T).
 //
-// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 32 tiles, four warps.  float32: FFMA with k
+// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 32 tiles through a three-stage cp.async ring, four warps.  float32: FFMA with k
 // ascending for every output element, so a row's result does not depend on what else is in the batch.
 #include <algorithm>
 
@@ -32,7 +32,13 @@ struct GroupedArgs {
     const int* seg;
     int M, N, K, G;
     int vec;   // rows of A and W start on 16 bytes and K is a multiple of 8 (bfloat16) / 4 (float32)
+    int il;    // the gated epilogue's two matrices are one, gate and up rows alternating in runs of 8 (W2 unused)
 };
+
+// Row n of the gate (up = false) or up (up = true) matrix inside a group's weight.
+__device__ __forceinline__ int64_t gated_row(const GroupedArgs& p, int n, bool up) {
+    return p.il ? (int64_t)(n >> 3) * 16 + (n & 7) + (up ? 8 : 0) : n;
+}
 
 // Which group and which rows of the list this CTA has; false if it has none.
 __device__ __forceinline__ bool find_tile(const GroupedArgs& p, int& g, int& row0, int& row_end) {
@@ -68,9 +74,10 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// rows x 32 bfloat16 of `src` (row r at src_row(r), null rows zero) into a padded tile.
+// rows x 32 bfloat16 of `src` (row r at src_row(r), null rows zero) into a padded tile.  With `vec` the chunks of 8 travel as
+// asynchronous 16-byte copies (the caller commits and waits); otherwise element by element.
 template <typename RowFn>
-__device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], RowFn src_row, int k0, int K, int vec) {
+__device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], RowFn src_row, int k0, int K, int vec, const void* any_global) {
     const int tid = threadIdx.x;
     if (vec) {
         // 64 rows x 4 chunks of 8: two chunks a thread
@@ -78,9 +85,10 @@ __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], Row
         for (int e = 0; e < 2; ++e) {
             const int idx = tid + e * 128, r = idx >> 2, c = (idx & 3) * 8;
             const __nv_bfloat16* row = src_row(r);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row && k0 + c < K) v = *reinterpret_cast<const uint4*>(row + k0 + c);
-            *reinterpret_cast<uint4*>(&tile[r][c]) = v;
+            const bool there = row && k0 + c < K;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&tile[r][c]);
+            const void* src = there ? (const void*)(row + k0 + c) : any_global;   // a copy of zero bytes fills with zeros and reads nothing
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(there ? 16 : 0) : "memory");
         }
     } else {
         for (int idx = tid; idx < GG_BM * GB_BK; idx += 128) {
@@ -91,26 +99,30 @@ __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], Row
     }
 }
 
+constexpr int GB_STAGES = 3;
+
 template <bool SWIGLU>
 __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArgs p) {
     pdl_wait();
     pdl_launch_dependents();
     int g, row0, row_end;
     if (!find_tile(p, g, row0, row_end)) return;
-    __shared__ __align__(16) __nv_bfloat16 As[GG_BM][GB_LD];
-    __shared__ __align__(16) __nv_bfloat16 Ws[GG_BN][GB_LD];
-    __shared__ __align__(16) __nv_bfloat16 Us[SWIGLU ? GG_BN : 1][GB_LD];
+    __shared__ __align__(16) __nv_bfloat16 As[GB_STAGES][GG_BM][GB_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[GB_STAGES][GG_BN][GB_LD];
+    __shared__ __align__(16) __nv_bfloat16 Us[SWIGLU ? GB_STAGES : 1][SWIGLU ? GG_BN : 1][GB_LD];
+    __shared__ int64_t a_off[GG_BM];   // where each row of the tile starts in A (-1: beyond the group's rows)
     const int n0 = blockIdx.x * GG_BN;
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.A + p.a_group_cols * g;
     const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + p.w_group_stride * g;
-    const __nv_bfloat16* U = SWIGLU ? (const __nv_bfloat16*)p.W2 + p.w_group_stride * g : nullptr;
-    auto a_row = [&](int r) -> const __nv_bfloat16* {
-        const int lr = row0 + r;
-        if (lr >= row_end) return nullptr;
-        return A + (int64_t)(p.a_rows ? p.a_rows[lr] : lr) * p.lda;
-    };
-    auto w_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? W + (int64_t)(n0 + r) * p.ldw : nullptr; };
-    auto u_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? U + (int64_t)(n0 + r) * p.ldw : nullptr; };
+    const __nv_bfloat16* U = SWIGLU ? (p.il ? W : (const __nv_bfloat16*)p.W2 + p.w_group_stride * g) : nullptr;
+    if (threadIdx.x < GG_BM) {
+        const int lr = row0 + threadIdx.x;
+        a_off[threadIdx.x] = lr < row_end ? (int64_t)(p.a_rows ? p.a_rows[lr] : lr) * p.lda : -1;
+    }
+    __syncthreads();
+    auto a_row = [&](int r) -> const __nv_bfloat16* { return a_off[r] >= 0 ? A + a_off[r] : nullptr; };
+    auto w_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? W + gated_row(p, n0 + r, false) * p.ldw : nullptr; };
+    auto u_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? U + gated_row(p, n0 + r, true) * p.ldw : nullptr; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
@@ -125,39 +137,49 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
                 if (SWIGLU) acu[i][j][e] = 0.f;
             }
 
-    for (int k0 = 0; k0 < p.K; k0 += GB_BK) {
-        load_tile_bf16(As, a_row, k0, p.K, p.vec);
-        load_tile_bf16(Ws, w_row, k0, p.K, p.vec);
-        if (SWIGLU) load_tile_bf16(Us, u_row, k0, p.K, p.vec);
-        __syncthreads();
+    const int n_k = (p.K + GB_BK - 1) / GB_BK;
+    auto fetch = [&](int kb) {
+        if (kb < n_k) {
+            const int st = kb % GB_STAGES;
+            load_tile_bf16(As[st], a_row, kb * GB_BK, p.K, p.vec, p.W);
+            load_tile_bf16(Ws[st], w_row, kb * GB_BK, p.K, p.vec, p.W);
+            if (SWIGLU) load_tile_bf16(Us[st], u_row, kb * GB_BK, p.K, p.vec, p.W);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per k-block, empty ones included: the wait counts groups
+    };
+    for (int kb = 0; kb < GB_STAGES - 1; ++kb) fetch(kb);
+    for (int kb = 0; kb < n_k; ++kb) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(GB_STAGES - 2) : "memory");
+        __syncthreads();                 // block kb has landed for everyone, and block kb - 1's stage is free again
+        fetch(kb + GB_STAGES - 1);
+        const int st = kb % GB_STAGES;
 #pragma unroll
         for (int kk = 0; kk < GB_BK; kk += 16) {
             uint32_t a[2][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int r = wm + i * 16 + gid;
-                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * tig]);
-                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * tig]);
-                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * tig + 8]);
-                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * tig + 8]);
+                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tig]);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tig]);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tig + 8]);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tig + 8]);
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int n = wn + j * 8 + gid;
                 uint32_t b[2];
-                b[0] = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + 2 * tig]);
-                b[1] = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + 2 * tig + 8]);
+                b[0] = *reinterpret_cast<const uint32_t*>(&Ws[st][n][kk + 2 * tig]);
+                b[1] = *reinterpret_cast<const uint32_t*>(&Ws[st][n][kk + 2 * tig + 8]);
 #pragma unroll
                 for (int i = 0; i < 2; ++i) mma_bf16(acc[i][j], a[i], b);
                 if (SWIGLU) {
-                    b[0] = *reinterpret_cast<const uint32_t*>(&Us[n][kk + 2 * tig]);
-                    b[1] = *reinterpret_cast<const uint32_t*>(&Us[n][kk + 2 * tig + 8]);
+                    b[0] = *reinterpret_cast<const uint32_t*>(&Us[st][n][kk + 2 * tig]);
+                    b[1] = *reinterpret_cast<const uint32_t*>(&Us[st][n][kk + 2 * tig + 8]);
 #pragma unroll
                     for (int i = 0; i < 2; ++i) mma_bf16(acu[i][j], a[i], b);
                 }
             }
         }
-        __syncthreads();
     }
     __nv_bfloat16* C = (__nv_bfloat16*)p.C + p.c_group_cols * g;
 #pragma unroll
@@ -196,7 +218,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_f32_kernel(const GroupedArgs
     const int n0 = blockIdx.x * GG_BN;
     const float* A = (const float*)p.A + p.a_group_cols * g;
     const float* W = (const float*)p.W + p.w_group_stride * g;
-    const float* U = SWIGLU ? (const float*)p.W2 + p.w_group_stride * g : nullptr;
+    const float* U = SWIGLU ? (p.il ? W : (const float*)p.W2 + p.w_group_stride * g) : nullptr;
     const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
     float acc[4][4], acu[SWIGLU ? 4 : 1][4];
 #pragma unroll
@@ -220,8 +242,8 @@ __global__ void __launch_bounds__(256) grouped_gemm_f32_kernel(const GroupedArgs
             const int r = idx / GF_BK, kk = idx % GF_BK;
             const int gn = n0 + r, gk = k0 + kk;
             As[kk][r] = (a_off[e] >= 0 && gk < p.K) ? A[a_off[e] + gk] : 0.f;
-            Ws[kk][r] = (gn < p.N && gk < p.K) ? W[(int64_t)gn * p.ldw + gk] : 0.f;
-            if (SWIGLU) Us[kk][r] = (gn < p.N && gk < p.K) ? U[(int64_t)gn * p.ldw + gk] : 0.f;
+            Ws[kk][r] = (gn < p.N && gk < p.K) ? W[gated_row(p, gn, false) * p.ldw + gk] : 0.f;
+            if (SWIGLU) Us[kk][r] = (gn < p.N && gk < p.K) ? U[gated_row(p, gn, true) * p.ldw + gk] : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -259,19 +281,22 @@ __global__ void __launch_bounds__(256) grouped_gemm_f32_kernel(const GroupedArgs
 
 }  // namespace
 
-// A: activations (dtype), rows lda apart.  W (and W2 with swiglu): [G][N, K], groups w_group_stride elements apart,
-// rows ldw apart.  C: rows ldc apart.  seg == null: uniform groups of M rows each; else the list has M rows in all.
+// A: activations (dtype), rows lda apart.  W (and W2 with swiglu == 1): [G][N, K], groups w_group_stride elements apart,
+// rows ldw apart; swiglu == 2: W is [G][2N, K] with gate and up rows alternating in runs of 8 (W2 unused, N a multiple
+// of 8).  C: rows ldc apart.  seg == null: uniform groups of M rows each; else the list has M rows in all.
 IMP_API int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const void* A, int64_t lda, int64_t a_group_cols,
                              const int* a_rows, const void* W, const void* W2, int64_t w_group_stride, int64_t ldw, const int* seg,
                              int M, int N, int K, int G, int swiglu, int dtype, void* stream) {
     if (M == 0 || N == 0 || G == 0) return 0;
     IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0 && G > 0, "imp_grouped_gemm: bad argument");
-    IMP_CHECK_ARG(!swiglu || W2, "imp_grouped_gemm: the gated epilogue needs a second weight");
+    IMP_CHECK_ARG(swiglu != 1 || W2, "imp_grouped_gemm: the gated epilogue needs a second weight");
+    IMP_CHECK_ARG(swiglu != 2 || N % 8 == 0, "imp_grouped_gemm: interleaved gate and up rows come in runs of 8");
     GroupedArgs p;
     p.A = A, p.lda = lda, p.a_rows = a_rows, p.a_group_cols = a_group_cols;
     p.W = W, p.W2 = W2, p.w_group_stride = w_group_stride, p.ldw = ldw;
     p.C = C, p.ldc = ldc, p.c_group_cols = c_group_cols, p.seg = seg;
     p.M = M, p.N = N, p.K = K, p.G = G;
+    p.il = swiglu == 2 ? 1 : 0;
     const int el = dtype == IMP_F32 ? 4 : 2, per16 = 16 / el;
     auto aligned = [&](const void* q) { return q == nullptr || (uintptr_t)q % 16 == 0; };
     p.vec = (K % per16 == 0 && lda % per16 == 0 && ldw % per16 == 0 && a_group_cols % per16 == 0 && w_group_stride % per16 == 0 &&

@@ -141,6 +141,7 @@ int imp_wkv_output(void* y, const float* o, const void* g, int64_t ldg, const fl
 int imp_moe_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
                   int* idx, float* wts, float* gate, int act_dtype, void* stream);
 int imp_moe_sort(const int* idx, int n_tokens, int top, int E, int* seg, int* row_token, int* pair_row, void* stream);
+int imp_gather_rows(void* dst, const void* src, int64_t ld, const int* idx, int n_rows, int d, int dtype, void* stream);
 int imp_moe_combine(void* out, const void* y, const int* pair_row, const float* wts, int n_tokens, int top, const void* shared,
                     const float* gate, int d, int act_dtype, void* stream);
 }

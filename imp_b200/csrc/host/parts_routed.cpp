@@ -301,7 +301,8 @@ struct Wkv : Mixer {
 // params: hidden_size, num_experts, top_k, expert_size, shared_size (0: no shared expert).
 struct RoutedExperts : FeedForward {
     int64_t d, E, top, F, Fs;
-    Tensor w_gate, w_up, w_down;       // [E * F, d], [E * F, d], [E * d, F]
+    Tensor w_gate, w_up, w_down;       // [E * F, d], [E * F, d], [E * d, F]; or w_gate [E * 2F, d], gate and up rows alternating in runs of 8
+    bool interleaved = false;
     Tensor router, router_bias, sg;    // float32
     Tensor s_gu, s_down;               // the shared expert
     bool s_interleaved = false;
@@ -341,8 +342,19 @@ struct RoutedExperts : FeedForward {
             us.push_back(a.tensor("up_" + n));
             ds.push_back(a.tensor("down_" + n));
         }
-        w_gate = cat_rows(rt, *a.store, gs);
-        w_up = cat_rows(rt, *a.store, us);
+        // bfloat16 and F a multiple of 8: every expert's gate and up rows alternate in runs of 8, the layout of the fused
+        // gate-up product, so that an expert with many rows can go to that product (see forward)
+        interleaved = F % SWIGLU_INTERLEAVE == 0 && gs[0].dtype == BF16 && us[0].dtype == BF16;
+        if (interleaved) {
+            std::vector<Tensor> both;
+            for (int64_t e = 0; e < E; ++e) both.push_back(interleave_gate_up(rt, *a.store, gs[(size_t)e], us[(size_t)e]));
+            w_gate = cat_rows(rt, *a.store, both);
+            IMP_CUDA(cudaStreamSynchronize(rt.stream));
+            for (const Tensor& t : both) a.store->release(t.data);
+        } else {
+            w_gate = cat_rows(rt, *a.store, gs);
+            w_up = cat_rows(rt, *a.store, us);
+        }
         w_down = cat_rows(rt, *a.store, ds);
         router = to_float32(rt, *a.store, a.tensor("router"));
         router_bias = to_float32(rt, *a.store, a.tensor("router_bias"));
@@ -382,13 +394,42 @@ struct RoutedExperts : FeedForward {
                      "moe_route");
         check_launch(imp_moe_sort(idx, (int)T, (int)top, (int)E, seg, row_token, pair_row, rt.stream), "moe_sort");
         Tensor act = rt.empty(P, F);
-        check_launch(imp_grouped_gemm(act.data, F, 0, x.data, x.stride0, 0, row_token, w_gate.data, w_up.data, F * d, d, seg, (int)P, (int)F, (int)d,
-                                      (int)E, 1, dt, rt.stream),
-                     "grouped_gemm (experts, gate and up)");
         Tensor y = rt.empty(P, d);
-        check_launch(imp_grouped_gemm(y.data, d, 0, act.data, F, 0, nullptr, w_down.data, nullptr, d * F, F, seg, (int)P, (int)d, (int)F, (int)E, 0, dt,
-                                      rt.stream),
-                     "grouped_gemm (experts, down)");
+        // Portions of prompts with much work an expert (rows x F x d of 2^31 and more on average): the list's offsets come to
+        // the host, and every expert's rows go to the tensor-memory products as a dense matrix (the wait costs one round
+        // trip a layer; 2,048 tokens on 16 experts of 4096 x 4096: 1.2 against 2.0 ms a layer; with experts of 1024 x 1024
+        // the products' fixed cost loses: 5.9 against 4.0 ms for four layers).  All other steps, and every step that may
+        // be captured into a graph, run the two products over groups, whose launches do not depend on the routing.
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        IMP_CUDA(cudaStreamIsCapturing(rt.stream, &capturing));
+        static const double dense_work = [] { const std::string e = env_string("IMP_B200_MOE_DENSE_WORK", ""); return e.empty() ? 2147483648.0 : std::atof(e.c_str()); }();
+        if (interleaved && !st.decode_only() && capturing == cudaStreamCaptureStatusNone && dense_work > 0 &&
+            (double)P / (double)E * (double)F * (double)d >= dense_work) {
+            std::vector<int> hseg((size_t)E + 1);
+            Tensor xs = rt.empty(P, d);
+            check_launch(imp_gather_rows(xs.data, x.data, x.stride0, row_token, (int)P, (int)d, dt, rt.stream), "gather_rows");
+            IMP_CUDA(cudaMemcpyAsync(hseg.data(), seg, hseg.size() * 4, cudaMemcpyDeviceToHost, rt.stream));
+            IMP_CUDA(cudaStreamSynchronize(rt.stream));
+            const size_t el = elem_size(rt.dtype);
+            for (int64_t e = 0; e < E; ++e) {
+                const int64_t a0 = hseg[(size_t)e], n = hseg[(size_t)e + 1] - a0;
+                if (n <= 0) continue;
+                Tensor xe = tensor2d((char*)xs.data + (size_t)(a0 * d) * el, rt.dtype, n, d);
+                Tensor ae = tensor2d((char*)act.data + (size_t)(a0 * F) * el, rt.dtype, n, F);
+                Tensor ye = tensor2d((char*)y.data + (size_t)(a0 * d) * el, rt.dtype, n, d);
+                Tensor wgu = tensor2d((char*)w_gate.data + (size_t)(e * 2 * F * d) * el, w_gate.dtype, 2 * F, d);
+                Tensor wd = tensor2d((char*)w_down.data + (size_t)(e * d * F) * el, w_down.dtype, d, F);
+                linear_swiglu(rt, ae, xe, wgu);
+                linear(rt, ye, ae, wd);
+            }
+        } else {
+            check_launch(imp_grouped_gemm(act.data, F, 0, x.data, x.stride0, 0, row_token, w_gate.data, interleaved ? nullptr : w_up.data,
+                                          (interleaved ? 2 : 1) * F * d, d, seg, (int)P, (int)F, (int)d, (int)E, interleaved ? 2 : 1, dt, rt.stream),
+                         "grouped_gemm (experts, gate and up)");
+            check_launch(imp_grouped_gemm(y.data, d, 0, act.data, F, 0, nullptr, w_down.data, nullptr, d * F, F, seg, (int)P, (int)d, (int)F, (int)E, 0,
+                                          dt, rt.stream),
+                         "grouped_gemm (experts, down)");
+        }
         Tensor shared{};
         if (Fs > 0) {
             Tensor sa = rt.empty(T, Fs);

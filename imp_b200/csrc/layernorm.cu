@@ -75,6 +75,105 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_kernel(float* __restri
     }
 }
 
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+// Rows whose width is a multiple of 4, up to 256 x NV x 4 columns: the row is read once with 16-byte loads issued together,
+// kept in registers (NV float4 a thread) and written from there.
+template <typename TA, typename TW, int NV>
+__global__ void __launch_bounds__(LN_BLOCK) add_layernorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ branch,
+                                                                     const float* __restrict__ col_scale, const TW* __restrict__ w,
+                                                                     TA* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+                                                                     int write_h) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int64_t src = rows ? rows[r] : r;
+    float* hrow = h + src * d;
+    const TA* brow = branch ? branch + src * d : nullptr;
+    float4 v[NV];
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+        const int i = (threadIdx.x + e * LN_BLOCK) * 4;
+        v[e] = i < d ? Vec4<float>::load(hrow + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (brow) {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const int i = (threadIdx.x + e * LN_BLOCK) * 4;
+            if (i < d) {
+                const float4 b = Vec4<TA>::load(brow + i);
+                if (col_scale) {
+                    const float4 s = Vec4<float>::load(col_scale + i);
+                    v[e].x = fmaf(s.x, b.x, v[e].x), v[e].y = fmaf(s.y, b.y, v[e].y), v[e].z = fmaf(s.z, b.z, v[e].z), v[e].w = fmaf(s.w, b.w, v[e].w);
+                } else {
+                    v[e].x += b.x, v[e].y += b.y, v[e].z += b.z, v[e].w += b.w;
+                }
+                if (write_h) Vec4<float>::store(hrow + i, v[e]);
+            }
+        }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < NV; ++e) sum += (v[e].x + v[e].y) + (v[e].z + v[e].w);
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+        const int i = (threadIdx.x + e * LN_BLOCK) * 4;
+        if (i < d) {
+            const float a = v[e].x - mean, b = v[e].y - mean, c = v[e].z - mean, g = v[e].w - mean;
+            ss += (a * a + b * b) + (c * c + g * g);
+        }
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+    TA* orow = out + (int64_t)r * d;
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+        const int i = (threadIdx.x + e * LN_BLOCK) * 4;
+        if (i < d) {
+            const float4 ww = Vec4<TW>::load(w + i);
+            Vec4<TA>::store(orow + i, make_float4((v[e].x - mean) * inv * ww.x, (v[e].y - mean) * inv * ww.y, (v[e].z - mean) * inv * ww.z,
+                                                  (v[e].w - mean) * inv * ww.w));
+        }
+    }
+}
+
+template <typename TA, typename TW>
+static cudaError_t launch_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows, int n, int d,
+                                    float eps, int write_h, cudaStream_t s) {
+    const dim3 grid(n), block(LN_BLOCK);
+    const bool vec = d % 4 == 0 && d <= LN_BLOCK * 4 * 8 && (uintptr_t)h % 16 == 0 && (uintptr_t)branch % 8 == 0 && (uintptr_t)out % 8 == 0 &&
+                     (uintptr_t)w % 16 == 0 && (uintptr_t)col_scale % 16 == 0;
+    if (vec) {
+        const int nv = (d / 4 + LN_BLOCK - 1) / LN_BLOCK;
+        if (nv <= 1) return imp_launch(add_layernorm_vec_kernel<TA, TW, 1>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+        if (nv <= 2) return imp_launch(add_layernorm_vec_kernel<TA, TW, 2>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+        if (nv <= 4) return imp_launch(add_layernorm_vec_kernel<TA, TW, 4>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+        return imp_launch(add_layernorm_vec_kernel<TA, TW, 8>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+    }
+    return imp_launch(add_layernorm_kernel<TA, TW>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+}
+
 // h: [*, d] float32 stream; branch (optional, dense [*, d] of the activation type) is added first, times col_scale
 // (optional float32 [d]).  rows: optional gather list (then h is left as it is: write_h must be 0).
 IMP_API int imp_add_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows,
@@ -83,23 +182,13 @@ IMP_API int imp_add_layernorm(float* h, const void* branch, const float* col_sca
     IMP_CHECK_ARG(h && w && out && d > 0 && n_out_rows > 0, "imp_add_layernorm: bad argument");
     IMP_CHECK_ARG(!(rows && write_h), "imp_add_layernorm: a gather list and write_h exclude each other");
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_out_rows), block(LN_BLOCK);
     cudaError_t e;
-    if (act_dtype == IMP_F32) {
-        if (w_dtype == IMP_F32)
-            e = imp_launch(add_layernorm_kernel<float, float>, grid, block, 0, s, h, (const float*)branch, col_scale, (const float*)w,
-                           (float*)out, rows, d, eps, write_h);
-        else
-            e = imp_launch(add_layernorm_kernel<float, __nv_bfloat16>, grid, block, 0, s, h, (const float*)branch, col_scale,
-                           (const __nv_bfloat16*)w, (float*)out, rows, d, eps, write_h);
-    } else {
-        if (w_dtype == IMP_F32)
-            e = imp_launch(add_layernorm_kernel<__nv_bfloat16, float>, grid, block, 0, s, h, (const __nv_bfloat16*)branch, col_scale,
-                           (const float*)w, (__nv_bfloat16*)out, rows, d, eps, write_h);
-        else
-            e = imp_launch(add_layernorm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, h, (const __nv_bfloat16*)branch,
-                           col_scale, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, rows, d, eps, write_h);
-    }
+    if (act_dtype == IMP_F32)
+        e = w_dtype == IMP_F32 ? launch_layernorm<float, float>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s)
+                               : launch_layernorm<float, __nv_bfloat16>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s);
+    else
+        e = w_dtype == IMP_F32 ? launch_layernorm<__nv_bfloat16, float>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s)
+                               : launch_layernorm<__nv_bfloat16, __nv_bfloat16>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s);
     if (e != cudaSuccess) {
         imp_set_error("imp_add_layernorm: %s", cudaGetErrorString(e));
         return (int)e;

@@ -13,63 +13,119 @@
 
 namespace {
 
-constexpr int ROUTE_BLOCK = 128, ROUTE_MAX_E = 1024, ROUTE_MAX_TOP = 32;
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
 
-template <typename TA>
-__global__ void __launch_bounds__(ROUTE_BLOCK) moe_route_kernel(const TA* __restrict__ x, int64_t ldx, int d, const float* __restrict__ wr,
-                                                               const float* __restrict__ br, int E, int top, const float* __restrict__ wg,
-                                                               int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ gate) {
+constexpr int ROUTE_BLOCK = 256, ROUTE_MAX_E = 1024, ROUTE_MAX_TOP = 32;
+
+// A CTA routes TPB tokens: their rows wait in shared memory as 32-bit values while each warp walks the router's rows (and
+// the shared expert's mixing row), one row at a time against all TPB tokens, so a row of the router is read once per CTA.
+// A token's sums are made the same way whatever TPB is: lane-strided partial sums of four-wide pieces, then a shuffle tree.
+template <typename TA, int TPB>
+__global__ void __launch_bounds__(ROUTE_BLOCK) moe_route_kernel(const TA* __restrict__ x, int64_t ldx, int n_tokens, int d,
+                                                               const float* __restrict__ wr, const float* __restrict__ br, int E, int top,
+                                                               const float* __restrict__ wg, int* __restrict__ idx, float* __restrict__ wts,
+                                                               float* __restrict__ gate, int vec) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float sm[];   // x [d], then z [E]
+    extern __shared__ __align__(16) float sm[];   // x [TPB][d4], then z [TPB][E]
+    const int d4 = (d + 3) & ~3;
     float* xs = sm;
-    float* z = sm + d;
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const TA* row = x + (int64_t)t * ldx;
-    for (int i = tid; i < d; i += ROUTE_BLOCK) xs[i] = to_float(row[i]);
+    float* z = sm + (size_t)TPB * d4;
+    const int t0 = blockIdx.x * TPB, nt = min(TPB, n_tokens - t0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < TPB * d4; e += ROUTE_BLOCK) {
+        const int tk = e / d4, i = e % d4;
+        xs[e] = (tk < nt && i < d) ? to_float(x[(int64_t)(t0 + tk) * ldx + i]) : 0.f;
+    }
     __syncthreads();
     for (int e = warp; e < E + (wg ? 1 : 0); e += ROUTE_BLOCK / 32) {
         const float* w = e < E ? wr + (int64_t)e * d : wg;
-        float acc = 0.f;
-        for (int i = lane; i < d; i += 32) acc = fmaf(xs[i], w[i], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            if (e < E) z[e] = acc + (br ? br[e] : 0.f);
-            else gate[t] = 1.f / (1.f + expf(-acc));
+        float acc[TPB];
+#pragma unroll
+        for (int tk = 0; tk < TPB; ++tk) acc[tk] = 0.f;
+        if (vec) {
+#pragma unroll 4
+            for (int i = lane * 4; i < d; i += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + i);
+#pragma unroll
+                for (int tk = 0; tk < TPB; ++tk) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xs + tk * d4 + i);
+                    acc[tk] = fmaf(xv.x, wv.x, acc[tk]);
+                    acc[tk] = fmaf(xv.y, wv.y, acc[tk]);
+                    acc[tk] = fmaf(xv.z, wv.z, acc[tk]);
+                    acc[tk] = fmaf(xv.w, wv.w, acc[tk]);
+                }
+            }
+        } else {
+            for (int i = lane; i < d; i += 32) {
+                const float wv = w[i];
+#pragma unroll
+                for (int tk = 0; tk < TPB; ++tk) acc[tk] = fmaf(xs[tk * d4 + i], wv, acc[tk]);
+            }
+        }
+#pragma unroll
+        for (int tk = 0; tk < TPB; ++tk) {
+            const float sum = warp_sum(acc[tk]);
+            if (lane == 0 && tk < nt) {
+                if (e < E) z[tk * E + e] = sum + (br ? br[e] : 0.f);
+                else gate[t0 + tk] = 1.f / (1.f + expf(-sum));
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) return;
-    // `top` rounds of arg-max over the logits that are left; the lower index wins a tie
-    float chosen[ROUTE_MAX_TOP];
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int at = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (v > best) best = v, at = e;     // ascending e: the first of equal values stays
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
-        }
-        chosen[k] = best;
-        if (lane == 0) {
-            idx[(int64_t)t * top + k] = at;
-            z[at] = -INFINITY;
-        }
-        __syncwarp();
-    }
-    if (lane == 0) {
-        const float largest = chosen[0];   // the first chosen is the largest
-        float sum = 0.f;
+    // `top` rounds of arg-max over the logits that are left, a warp per token; the lower index wins a tie
+    for (int tk = warp; tk < nt; tk += ROUTE_BLOCK / 32) {
+        float* zt = z + tk * E;
+        const int64_t t = t0 + tk;
+        float chosen[ROUTE_MAX_TOP];
         for (int k = 0; k < top; ++k) {
-            chosen[k] = expf(chosen[k] - largest);
-            sum += chosen[k];
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = zt[e];
+                if (v > best) best = v, at = e;     // ascending e: the first of equal values stays
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
+            }
+            chosen[k] = best;
+            if (lane == 0) {
+                idx[t * top + k] = at;
+                zt[at] = -INFINITY;
+            }
+            __syncwarp();
         }
-        for (int k = 0; k < top; ++k) wts[(int64_t)t * top + k] = chosen[k] / sum;
+        if (lane == 0) {
+            const float largest = chosen[0];   // the first chosen is the largest
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) {
+                chosen[k] = expf(chosen[k] - largest);
+                sum += chosen[k];
+            }
+            for (int k = 0; k < top; ++k) wts[t * top + k] = chosen[k] / sum;
+        }
     }
 }
 
@@ -124,15 +180,93 @@ __global__ void moe_combine_kernel(TA* __restrict__ out, const TA* __restrict__ 
     pdl_wait();
     pdl_launch_dependents();
     const int64_t t = blockIdx.x;
+    const float gt = gate ? gate[t] : 1.f;
+    if ((d & 3) == 0) {
+        // four columns a thread (rows start on 8 or 16 bytes: dense [*, d] with d a multiple of 4)
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float wk = wts[t * top + k];
+                const float4 v = Vec4<TA>::load(y + (int64_t)pair_row[t * top + k] * d + i);
+                acc.x = fmaf(wk, v.x, acc.x), acc.y = fmaf(wk, v.y, acc.y), acc.z = fmaf(wk, v.z, acc.z), acc.w = fmaf(wk, v.w, acc.w);
+            }
+            if (shared) {
+                const float4 v = Vec4<TA>::load(shared + t * d + i);
+                acc.x = fmaf(gt, v.x, acc.x), acc.y = fmaf(gt, v.y, acc.y), acc.z = fmaf(gt, v.z, acc.z), acc.w = fmaf(gt, v.w, acc.w);
+            }
+            Vec4<TA>::store(out + t * d + i, acc);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], to_float(y[(int64_t)pair_row[t * top + k] * d + i]), acc);
-        if (shared) acc = fmaf(gate ? gate[t] : 1.f, to_float(shared[t * d + i]), acc);
+        if (shared) acc = fmaf(gt, to_float(shared[t * d + i]), acc);
         out[t * d + i] = from_float<TA>(acc);
     }
 }
 
+// dst[r] = src[idx[r]]: rows of d values, 16 bytes a thread where the rows allow it.
+template <typename TA>
+__global__ void gather_rows_kernel(TA* __restrict__ dst, const TA* __restrict__ src, int64_t ld, const int* __restrict__ idx, int d, int vec) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t r = blockIdx.x;
+    const TA* from = src + (int64_t)idx[r] * ld;
+    TA* to = dst + r * d;
+    if (vec) {
+        constexpr int PER = 16 / (int)sizeof(TA);
+        for (int i = threadIdx.x * PER; i < d; i += blockDim.x * PER) *reinterpret_cast<uint4*>(to + i) = *reinterpret_cast<const uint4*>(from + i);
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) to[i] = from[i];
+    }
+}
+
 }  // namespace
+
+IMP_API int imp_gather_rows(void* dst, const void* src, int64_t ld, const int* idx, int n_rows, int d, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(dst && src && idx && d > 0, "imp_gather_rows: bad argument");
+    const int el = dtype == IMP_F32 ? 4 : 2;
+    const int vec = ((int64_t)d * el % 16 == 0 && ld * el % 16 == 0 && (uintptr_t)dst % 16 == 0 && (uintptr_t)src % 16 == 0) ? 1 : 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = dtype == IMP_F32 ? imp_launch(gather_rows_kernel<float>, dim3(n_rows), dim3(128), 0, s, (float*)dst, (const float*)src, ld, idx, d, vec)
+                                     : imp_launch(gather_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, s, (__nv_bfloat16*)dst,
+                                                  (const __nv_bfloat16*)src, ld, idx, d, vec);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_gather_rows: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+template <typename TA, int TPB>
+static cudaError_t launch_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
+                                int* idx, float* wts, float* gate, int vec, size_t smem, cudaStream_t s) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<TA, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return imp_launch(moe_route_kernel<TA, TPB>, dim3((n_tokens + TPB - 1) / TPB), dim3(ROUTE_BLOCK), smem, s, (const TA*)x, ldx, n_tokens, d, wr, br,
+                      E, top, wg, idx, wts, gate, vec);
+}
+
+template <typename TA>
+static cudaError_t route_by_size(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
+                                 int* idx, float* wts, float* gate, int vec, cudaStream_t s) {
+    // more tokens a CTA where there are many (a row of the router is read once per CTA), one where there are few (more CTAs)
+    int tpb = n_tokens >= 1024 ? 8 : n_tokens >= 256 ? 4 : n_tokens >= 64 ? 2 : 1;
+    const int d4 = (d + 3) & ~3;
+    auto bytes = [&](int t) { return ((size_t)t * d4 + (size_t)t * E) * 4; };
+    while (tpb > 1 && bytes(tpb) > 160 * 1024) tpb /= 2;
+    if (bytes(tpb) > 200 * 1024) return cudaErrorInvalidValue;
+    switch (tpb) {
+        case 8: return launch_route<TA, 8>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(8), s);
+        case 4: return launch_route<TA, 4>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(4), s);
+        case 2: return launch_route<TA, 2>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(2), s);
+        default: return launch_route<TA, 1>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(1), s);
+    }
+}
 
 // x [T, d] (activation type, rows ldx apart); wr float32 [E, d], br float32 [E] or null; wg float32 [d] or null (then
 // gate is not written).  idx int32 [T, top], wts float32 [T, top], gate float32 [T].
@@ -142,20 +276,12 @@ IMP_API int imp_moe_route(const void* x, int64_t ldx, int n_tokens, int d, const
     IMP_CHECK_ARG(x && wr && idx && wts && d > 0 && (!wg || gate), "imp_moe_route: bad argument");
     IMP_CHECK_ARG(E > 0 && E <= ROUTE_MAX_E && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                   "imp_moe_route: %d experts (at most %d), %d chosen (at most %d and no more than there are)", E, ROUTE_MAX_E, top, ROUTE_MAX_TOP);
-    const size_t smem = (size_t)(d + E) * 4;
-    IMP_CHECK_ARG(smem <= 200 * 1024, "imp_moe_route: rows of %d values do not fit the shared memory", d);
+    const int vec = (d % 4 == 0 && (uintptr_t)wr % 16 == 0 && (!wg || (uintptr_t)wg % 16 == 0)) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e;
-    if (act_dtype == IMP_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = imp_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(ROUTE_BLOCK), smem, s, (const float*)x, ldx, d, wr, br, E, top, wg, idx, wts, gate);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = imp_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(ROUTE_BLOCK), smem, s, (const __nv_bfloat16*)x, ldx, d, wr, br, E,
-                       top, wg, idx, wts, gate);
-    }
+    cudaError_t e = act_dtype == IMP_F32 ? route_by_size<float>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, s)
+                                         : route_by_size<__nv_bfloat16>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, s);
     if (e != cudaSuccess) {
-        imp_set_error("imp_moe_route: %s", cudaGetErrorString(e));
+        imp_set_error("imp_moe_route: %s (rows of %d values, %d experts)", cudaGetErrorString(e), d, E);
         return (int)e;
     }
     return 0;

@@ -8,8 +8,8 @@
 //   S        = diag(w[t]) S + k[t] v[t]^T
 //   y[t]     = o[t] / sqrt(mean(o[t]^2) + eps) * g_norm * gate[t]     per head
 //
-// Everything but the projections is 32-bit.  The scan gives a (sequence, head) to one CTA; a column of S (one value
-// channel) is spread over four lanes, each with every fourth key row in registers, so a token costs D/4
+// Everything but the projections is 32-bit.  The scan gives 32 value columns of a (sequence, head) to one CTA; a column
+// of S is spread over four lanes, each with a quarter of the key rows in registers, so a token costs D/4
 // multiply-adds a lane for the read-out, as many for the update, and two shuffles.  Inputs come in chunks of
 // 16 tokens through shared memory.  The order of every sum depends on D alone: a token's result is the same bits
 // however the prompt is cut and whatever else is in the batch.
@@ -69,71 +69,138 @@ template <typename TA> __global__ void tanh_kernel(TA* __restrict__ x, int64_t n
 }
 
 // ------------------------------------------------------------------------------------------------- scan
-constexpr int WKV_LANES = 4;
+// A CTA owns WKV_COLS value columns of one head's S for one sequence; a column is spread over four lanes, each with a
+// contiguous quarter of the key rows in registers.  The token's r, w and k are read from shared memory four at a time.
+constexpr int WKV_LANES = 4, WKV_COLS = 32;
 
 template <typename TA, int RPT>
-__global__ void __launch_bounds__(RPT * 16) wkv_scan_kernel(const TA* __restrict__ r, const TA* __restrict__ k, const TA* __restrict__ v,
-                                                             int64_t ld, const float* __restrict__ dlog, const float* __restrict__ w0,
-                                                             const float* __restrict__ u, float* __restrict__ state, float* __restrict__ out,
-                                                             const int* __restrict__ q_start, const int* __restrict__ slots, int H, int D) {
+__global__ void __launch_bounds__(WKV_COLS* WKV_LANES) wkv_scan_kernel(const TA* __restrict__ r, const TA* __restrict__ k, const TA* __restrict__ v,
+                                                                        int64_t ld, const float* __restrict__ dlog, const float* __restrict__ w0,
+                                                                        const float* __restrict__ u, float* __restrict__ state,
+                                                                        float* __restrict__ out, const int* __restrict__ q_start,
+                                                                        const int* __restrict__ slots, int H, int D, int col_blocks) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int DP = RPT * WKV_LANES;   // D rounded up to the rows the lanes hold
-    constexpr int WKV_CHUNK = RPT > 32 ? 8 : 16;   // five arrays of WKV_CHUNK x DP floats stay under 48 KB
-    __shared__ float s_r[WKV_CHUNK][DP], s_k[WKV_CHUNK][DP], s_w[WKV_CHUNK][DP], s_b[WKV_CHUNK][DP], s_v[WKV_CHUNK][DP];
-    const int h = blockIdx.x, seq = blockIdx.y;
+    constexpr int DP = RPT * WKV_LANES;   // D rounded up to the rows the four lanes hold (RPT a multiple of 4)
+    constexpr int WKV_CHUNK = RPT > 32 ? 8 : 16;   // three arrays of WKV_CHUNK x DP floats stay under 48 KB
+    // row i lives at i + 4 * (i / RPT): the four lanes of a column read 16 bytes each from four different groups of banks
+    constexpr int DPP = DP + 4 * WKV_LANES;
+    __shared__ __align__(16) float s_r[WKV_CHUNK][DPP], s_k[WKV_CHUNK][DPP], s_w[WKV_CHUNK][DPP];
+    __shared__ float s_v[WKV_CHUNK][WKV_COLS], s_b[WKV_CHUNK];
+    const int h = blockIdx.x / col_blocks, j0 = (blockIdx.x % col_blocks) * WKV_COLS, seq = blockIdx.y;
     const int t0 = q_start[seq], t1 = q_start[seq + 1];
     if (t1 <= t0) return;
-    const int tid = threadIdx.x, j = tid / WKV_LANES, sub = tid % WKV_LANES;
+    const int tid = threadIdx.x, j = j0 + tid / WKV_LANES, sub = tid % WKV_LANES, lane = tid & 31, warp = tid >> 5;
     const bool col = j < D;
     float* S = state + ((int64_t)slots[seq] * H + h) * D * D;
     float s[RPT];
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) {
-        const int i = sub + WKV_LANES * ii;
+        const int i = sub * RPT + ii;
         s[ii] = (col && i < D) ? S[(int64_t)i * D + j] : 0.f;
     }
     const int64_t hoff = (int64_t)h * D;
+    // The next chunk's inputs are asked for before the current chunk's tokens are walked and land in registers meanwhile:
+    // a CTA is alone on its SM with four warps, and a chunk read when it is needed would cost more than walking it.
+    constexpr int THREADS = WKV_COLS * WKV_LANES;
+    constexpr int NIT = WKV_CHUNK * DP / THREADS, NVI = WKV_CHUNK * WKV_COLS / THREADS;
+    TA pr[NIT], pk[NIT], pv[NVI];
+    float pd[NIT];
+    auto prefetch = [&](int c0) {
+        const int n = min(WKV_CHUNK, t1 - c0);
+#pragma unroll
+        for (int it = 0; it < NIT; ++it) {
+            const int e = tid + it * THREADS, tt = e / DP, i = e % DP;
+            pr[it] = from_float<TA>(0.f), pk[it] = from_float<TA>(0.f), pd[it] = 0.f;
+            if (tt < n && i < D) {
+                const int64_t at = (int64_t)(c0 + tt) * ld + hoff + i;
+                pr[it] = r[at];
+                pk[it] = k[at];
+                pd[it] = dlog[(int64_t)(c0 + tt) * H * D + hoff + i];
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < NVI; ++it) {
+            const int e = tid + it * THREADS, tt = e / WKV_COLS, c = e % WKV_COLS;
+            pv[it] = (tt < n && j0 + c < D) ? v[(int64_t)(c0 + tt) * ld + hoff + j0 + c] : from_float<TA>(0.f);
+        }
+    };
+    prefetch(t0);
     for (int c0 = t0; c0 < t1; c0 += WKV_CHUNK) {
         const int n = min(WKV_CHUNK, t1 - c0);
         __syncthreads();   // the chunk before has been read
-        for (int e = tid; e < n * DP; e += blockDim.x) {
-            const int tt = e / DP, i = e % DP;
-            float rv = 0.f, kv = 0.f, wv = 1.f, vv = 0.f, bv = 0.f;
-            if (i < D) {
-                const int64_t at = (int64_t)(c0 + tt) * ld + hoff + i;
-                rv = to_float(r[at]);
-                kv = to_float(k[at]);
-                vv = to_float(v[at]);
-                wv = expf(-expf(dlog[(int64_t)(c0 + tt) * H * D + hoff + i] + w0[hoff + i]));
-                bv = rv * u[hoff + i] * kv;
-            }
-            s_r[tt][i] = rv, s_k[tt][i] = kv, s_w[tt][i] = wv, s_v[tt][i] = vv, s_b[tt][i] = bv;
+#pragma unroll
+        for (int it = 0; it < NIT; ++it) {
+            const int e = tid + it * THREADS, tt = e / DP, i = e % DP;
+            const int at = i + 4 * (i / RPT);
+            s_r[tt][at] = to_float(pr[it]);
+            s_k[tt][at] = to_float(pk[it]);
+            s_w[tt][at] = i < D ? expf(-expf(pd[it] + w0[hoff + i])) : 1.f;
+        }
+#pragma unroll
+        for (int it = 0; it < NVI; ++it) {
+            const int e = tid + it * THREADS;
+            s_v[e / WKV_COLS][e % WKV_COLS] = to_float(pv[it]);
         }
         __syncthreads();
-        for (int tt = 0; tt < n; ++tt) {
-            const float vj = col ? s_v[tt][j] : 0.f;
-            float a = 0.f, b = 0.f;
+        if (c0 + WKV_CHUNK < t1) prefetch(c0 + WKV_CHUNK);
+        // the bonus term's sum over the key rows, sum_i r_i u_i k_i: one warp per token, lanes stride the rows
+        for (int tt = warp; tt < n; tt += THREADS / 32) {
+            float b = 0.f;
+            for (int i = lane; i < D; i += 32) b = fmaf(s_r[tt][i + 4 * (i / RPT)] * u[hoff + i], s_k[tt][i + 4 * (i / RPT)], b);
+            b = warp_sum(b);
+            if (lane == 0) s_b[tt] = b;
+        }
+        __syncthreads();
+        // two tokens a round: both tokens' inputs are asked of shared memory before the first is used (four warps on
+        // an SM hide no latency for one another)
+        constexpr int NQ = RPT / 4;
+        const int base = sub * (RPT + 4);
+        auto fetch = [&](int tt, float4 (&R)[NQ], float4 (&W)[NQ], float4 (&K)[NQ], float& vj, float& bb) {
 #pragma unroll
-            for (int ii = 0; ii < RPT; ++ii) {
-                const int i = sub + WKV_LANES * ii;
-                a = fmaf(s_r[tt][i], s[ii], a);
-                b += s_b[tt][i];
+            for (int q = 0; q < NQ; ++q) {
+                R[q] = *reinterpret_cast<const float4*>(&s_r[tt][base + 4 * q]);
+                W[q] = *reinterpret_cast<const float4*>(&s_w[tt][base + 4 * q]);
+                K[q] = *reinterpret_cast<const float4*>(&s_k[tt][base + 4 * q]);
             }
-            float o = fmaf(vj, b, a);
+            vj = s_v[tt][tid / WKV_LANES];
+            bb = s_b[tt];
+        };
+        auto walk = [&](int tt, const float4 (&R)[NQ], const float4 (&W)[NQ], const float4 (&K)[NQ], float vj, float bb) {
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                a0 = fmaf(R[q].x, s[4 * q], a0);
+                a1 = fmaf(R[q].y, s[4 * q + 1], a1);
+                a0 = fmaf(R[q].z, s[4 * q + 2], a0);
+                a1 = fmaf(R[q].w, s[4 * q + 3], a1);
+            }
+            float o = a0 + a1;
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o = fmaf(vj, bb, o);
 #pragma unroll
-            for (int ii = 0; ii < RPT; ++ii) {
-                const int i = sub + WKV_LANES * ii;
-                s[ii] = fmaf(s_w[tt][i], s[ii], s_k[tt][i] * vj);
+            for (int q = 0; q < NQ; ++q) {
+                s[4 * q] = fmaf(W[q].x, s[4 * q], K[q].x * vj);
+                s[4 * q + 1] = fmaf(W[q].y, s[4 * q + 1], K[q].y * vj);
+                s[4 * q + 2] = fmaf(W[q].z, s[4 * q + 2], K[q].z * vj);
+                s[4 * q + 3] = fmaf(W[q].w, s[4 * q + 3], K[q].w * vj);
             }
             if (col && sub == 0) out[(int64_t)(c0 + tt) * H * D + hoff + j] = o;
+        };
+        for (int tt = 0; tt < n; tt += 2) {
+            float4 Ra[NQ], Wa[NQ], Ka[NQ], Rb[NQ], Wb[NQ], Kb[NQ];
+            float va, ba, vb, bb;
+            const bool two = tt + 1 < n;
+            fetch(tt, Ra, Wa, Ka, va, ba);
+            fetch(two ? tt + 1 : tt, Rb, Wb, Kb, vb, bb);
+            walk(tt, Ra, Wa, Ka, va, ba);
+            if (two) walk(tt + 1, Rb, Wb, Kb, vb, bb);
         }
     }
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) {
-        const int i = sub + WKV_LANES * ii;
+        const int i = sub * RPT + ii;
         if (col && i < D) S[(int64_t)i * D + j] = s[ii];
     }
 }
@@ -163,7 +230,9 @@ template <typename TA, int RPT>
 cudaError_t launch_scan(const void* r, const void* k, const void* v, int64_t ld, const float* dlog, const float* w0, const float* u,
                         float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, cudaStream_t s) {
     // an ordinary dependent: its CTAs hold many registers and would sit on the SMs while the kernels before it run
-    wkv_scan_kernel<TA, RPT><<<dim3(H, n_seqs), RPT * 16, 0, s>>>((const TA*)r, (const TA*)k, (const TA*)v, ld, dlog, w0, u, state, out, q_start, slots, H, D);
+    const int col_blocks = (D + WKV_COLS - 1) / WKV_COLS;
+    wkv_scan_kernel<TA, RPT><<<dim3(H * col_blocks, n_seqs), WKV_COLS * WKV_LANES, 0, s>>>((const TA*)r, (const TA*)k, (const TA*)v, ld, dlog, w0, u, state, out,
+                                                                                         q_start, slots, H, D, col_blocks);
     return cudaGetLastError();
 }
 
