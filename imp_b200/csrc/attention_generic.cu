@@ -24,7 +24,8 @@
 #include "common.cuh"
 
 constexpr int ATT_BLOCK = 128;
-constexpr int ATT_MAX_DH = 256;
+constexpr int ATT_MAX_DH = 1024;
+constexpr int ATT_ACC = ATT_MAX_DH / ATT_BLOCK;   // output entries a thread accumulates: tid, tid + 128, ...
 
 template <typename TA>
 __global__ void paged_attention_generic_kernel(
@@ -58,7 +59,9 @@ __global__ void paged_attention_generic_kernel(
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const float* bias_h = bias ? bias + (int64_t)h * n_dist : nullptr;
     float m = -INFINITY, l = 0.f;
-    float acc0 = 0.f, acc1 = 0.f;  // dims tid and tid + ATT_BLOCK
+    float acc[ATT_ACC];            // dims tid + a * ATT_BLOCK
+#pragma unroll
+    for (int a = 0; a < ATT_ACC; ++a) acc[a] = 0.f;
 
     for (int j0 = first; j0 <= pos; j0 += ATT_BLOCK) {
         const int j = j0 + tid;
@@ -86,17 +89,15 @@ __global__ void paged_attention_generic_kernel(
         l = l * corr + psum;
         m = m_new;
         const int n_here = min(ATT_BLOCK, pos - j0 + 1);
-        if (tid < Dh) {
-            float a = acc0 * corr;
-            for (int i = 0; i < n_here; ++i)
-                if (off_s[i] >= 0) a = fmaf(p_s[i], to_float(v_cache[off_s[i] + tid]), a);
-            acc0 = a;
-        }
-        if (tid + ATT_BLOCK < Dh) {
-            float a = acc1 * corr;
-            for (int i = 0; i < n_here; ++i)
-                if (off_s[i] >= 0) a = fmaf(p_s[i], to_float(v_cache[off_s[i] + tid + ATT_BLOCK]), a);
-            acc1 = a;
+#pragma unroll
+        for (int a = 0; a < ATT_ACC; ++a) {
+            const int dim = tid + a * ATT_BLOCK;
+            if (dim < Dh) {
+                float sum = acc[a] * corr;
+                for (int i = 0; i < n_here; ++i)
+                    if (off_s[i] >= 0) sum = fmaf(p_s[i], to_float(v_cache[off_s[i] + dim]), sum);
+                acc[a] = sum;
+            }
         }
         __syncthreads();  // p_s/off_s are rewritten by the next chunk
     }
@@ -106,12 +107,13 @@ __global__ void paged_attention_generic_kernel(
         const float m_new = fmaxf(m, sk);
         const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
         l = l * corr + expf(sk - m_new);
-        acc0 *= corr;
-        acc1 *= corr;
+#pragma unroll
+        for (int a = 0; a < ATT_ACC; ++a) acc[a] *= corr;
     }
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
-    if (tid < Dh) o[tid] = from_float<TA>(acc0 * inv_l);
-    if (tid + ATT_BLOCK < Dh) o[tid + ATT_BLOCK] = from_float<TA>(acc1 * inv_l);
+#pragma unroll
+    for (int a = 0; a < ATT_ACC; ++a)
+        if (tid + a * ATT_BLOCK < Dh) o[tid + a * ATT_BLOCK] = from_float<TA>(acc[a] * inv_l);
 }
 
 // out: [n_tokens, out_stride] (head h at column h*Dh); q likewise with q_stride.

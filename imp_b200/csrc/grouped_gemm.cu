@@ -9,7 +9,9 @@
 //              (rows / BM + groups); a CTA finds its group by walking seg, and leaves if there is no tile for it.
 // Optionally two weight matrices per group and the epilogue silu(A Wg^T) * (A Wu^T).
 //
-// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 32 tiles through a three-stage cp.async ring, four warps.  float32: FFMA with k
+// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 32 tiles through a cp.async ring of three or four stages,
+// fragments by ldmatrix, four warps.  (Tiles of 128 x 64 and 128 x 128 measured no faster for many rows a group and slower
+// for few.)  float32: FFMA with k
 // ascending for every output element, so a row's result does not depend on what else is in the batch.
 #include <algorithm>
 
@@ -99,12 +101,16 @@ __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], Row
     }
 }
 
-constexpr int GB_STAGES = 3;
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArgs p) {
     pdl_wait();
     pdl_launch_dependents();
+    constexpr int GB_STAGES = SWIGLU ? 3 : 4;   // 15 KB resp. 10 KB a stage
     int g, row0, row_end;
     if (!find_tile(p, g, row0, row_end)) return;
     __shared__ __align__(16) __nv_bfloat16 As[GB_STAGES][GG_BM][GB_LD];
@@ -126,6 +132,10 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    // what a lane hands to ldmatrix: for A (16 rows x 16 k) row lane % 16 at k + 8 * (lane / 16); for W (16 n x 16 k, two
+    // 8-column tiles of the product) row lane % 8 + 8 * (lane / 16) at k + 8 * ((lane / 8) % 2)
+    const int a_r = lane & 15, a_c = (lane >> 4) * 8;
+    const int b_r = (lane & 7) + (lane >> 4) * 8, b_c = ((lane >> 3) & 1) * 8;
     float acc[2][4][4], acu[SWIGLU ? 2 : 1][4][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
@@ -157,26 +167,25 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
         for (int kk = 0; kk < GB_BK; kk += 16) {
             uint32_t a[2][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int r = wm + i * 16 + gid;
-                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tig]);
-                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tig]);
-                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tig + 8]);
-                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tig + 8]);
-            }
+            for (int i = 0; i < 2; ++i) ldmatrix_x4(a[i], &As[st][wm + i * 16 + a_r][kk + a_c]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int n = wn + j * 8 + gid;
-                uint32_t b[2];
-                b[0] = *reinterpret_cast<const uint32_t*>(&Ws[st][n][kk + 2 * tig]);
-                b[1] = *reinterpret_cast<const uint32_t*>(&Ws[st][n][kk + 2 * tig + 8]);
+            for (int jj = 0; jj < 2; ++jj) {
+                uint32_t b[4];
+                ldmatrix_x4(b, &Ws[st][wn + jj * 16 + b_r][kk + b_c]);
+                const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
 #pragma unroll
-                for (int i = 0; i < 2; ++i) mma_bf16(acc[i][j], a[i], b);
+                for (int i = 0; i < 2; ++i) {
+                    mma_bf16(acc[i][2 * jj], a[i], b0);
+                    mma_bf16(acc[i][2 * jj + 1], a[i], b1);
+                }
                 if (SWIGLU) {
-                    b[0] = *reinterpret_cast<const uint32_t*>(&Us[st][n][kk + 2 * tig]);
-                    b[1] = *reinterpret_cast<const uint32_t*>(&Us[st][n][kk + 2 * tig + 8]);
+                    ldmatrix_x4(b, &Us[st][wn + jj * 16 + b_r][kk + b_c]);
+                    const uint32_t u0[2] = {b[0], b[1]}, u1[2] = {b[2], b[3]};
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) mma_bf16(acu[i][j], a[i], b);
+                    for (int i = 0; i < 2; ++i) {
+                        mma_bf16(acu[i][2 * jj], a[i], u0);
+                        mma_bf16(acu[i][2 * jj + 1], a[i], u1);
+                    }
                 }
             }
         }

@@ -86,6 +86,8 @@ struct LatentAttention : Mixer {
         Sizes s{need_int(p, "hidden_size", me), need_int(p, "num_heads", me), need_int(p, "head_dim", me), need_int(p, "rot_dim", me),
                 need_int(p, "value_dim", me), need_int(p, "kv_rank", me), need_int(p, "q_rank", me)};
         if (s.H <= 0 || s.D <= 0 || s.R <= 0 || s.Dv <= 0 || s.C <= 0 || s.Q <= 0) fail(IMP_ERROR_INVALID_MODEL, std::string(me) + ": every size must be positive");
+        if (s.C + s.R > 1024)
+            fail(IMP_ERROR_INVALID_MODEL, std::string(me) + ": kv_rank + rot_dim = " + std::to_string(s.C + s.R) + " exceeds the attention kernels' 1024 (tensor cores up to 256)");
         return s;
     }
     static TensorSpecs specs(const Json& p) {

@@ -122,6 +122,7 @@ LATENT_CASES = [
     dict(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=48, q_rank=24, d=64, page=16, base=100.0),
     dict(heads=2, dim=12, rot_dim=6, vdim=7, kv_rank=36, q_rank=10, d=40, page=8, base=10000.0),
     dict(heads=20, dim=16, rot_dim=16, vdim=8, kv_rank=16, q_rank=16, d=48, page=16, base=300.0),      # twenty heads on the one cached vector
+    dict(heads=2, dim=16, rot_dim=32, vdim=16, kv_rank=288, q_rank=16, d=48, page=16, base=1000.0),    # a cached vector of 320: beyond the tensor-core kernels
 ]
 
 
