@@ -1,10 +1,10 @@
 // True 32-bit matrix product  C[M,N] = A[M,K] * W[N,K]^T  (+ nothing else).
 //
 // The float32 path's only matrix kernel: plain FFMA, no tensor cores, no
-// reduced-precision mode.  Every output element is the fused-multiply-add
-// chain over k = 0..K-1 in ascending order, whatever M is and wherever the row
-// sits in the batch, so a token's result is bit-identical under every split of
-// the work.  The reference's fp32 route is cublasSgemm (src/compute/gemm.cu:
+// reduced-precision mode.  Every output element is summed over k in blocks of
+// 16 (a fused-multiply-add chain inside a block, ascending; the blocks' sums
+// added in ascending order), whatever M is and wherever the row sits in the
+// batch, so a token's result is bit-identical under every split of the work.  The reference's fp32 route is cublasSgemm (src/compute/gemm.cu:
 // 341-358) and a warp-per-row GEMV (src/compute/gemm.cu:452-493); W is stored
 // [N,K] as there (src/compute/gemm.h:18-19).
 #include "common.cuh"
@@ -39,6 +39,13 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ C, in
             Ws[kk][r] = (gn < N && gk < K) ? W[(int64_t)gn * ldw + gk] : 0.f;
         }
         __syncthreads();
+        // the 16 products of a block are summed on their own and then added to the running sum: the rounding of a long
+        // chain grows with its length, that of blocks with the square root of their number
+        float blk[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) blk[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < GF_BK; ++kk) {
             float a[4], w[4];
@@ -49,8 +56,12 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ C, in
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) blk[i][j] = fmaf(a[i], w[j], blk[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += blk[i][j];
         __syncthreads();
     }
 #pragma unroll

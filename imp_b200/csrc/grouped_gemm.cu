@@ -9,9 +9,9 @@
 //              (rows / BM + groups); a CTA finds its group by walking seg, and leaves if there is no tile for it.
 // Optionally two weight matrices per group and the epilogue silu(A Wg^T) * (A Wu^T).
 //
-// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 32 tiles through a cp.async ring of three or four stages,
+// bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 64 tiles through a cp.async ring of three or four stages,
 // fragments by ldmatrix, four warps.  (Tiles of 128 x 64 and 128 x 128 measured no faster for many rows a group and slower
-// for few.)  float32: FFMA with k
+// for few; skipping the products of 16-row pieces without rows measured slower too.)  float32: FFMA with k
 // ascending for every output element, so a row's result does not depend on what else is in the batch.
 #include <algorithm>
 
@@ -68,7 +68,7 @@ __device__ __forceinline__ bool find_tile(const GroupedArgs& p, int& g, int& row
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 
 // --------------------------------------------------------------------------------------- bfloat16
-constexpr int GB_BK = 32, GB_LD = GB_BK + 8;   // padded rows: fragment loads hit 32 different banks
+constexpr int GB_BK = 64, GB_LD = GB_BK + 8;   // a row of a block is a whole 128-byte line; padded rows: ldmatrix hits 32 different banks
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -82,10 +82,10 @@ template <typename RowFn>
 __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], RowFn src_row, int k0, int K, int vec, const void* any_global) {
     const int tid = threadIdx.x;
     if (vec) {
-        // 64 rows x 4 chunks of 8: two chunks a thread
+        // 64 rows x 8 chunks of 8: four chunks a thread
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int idx = tid + e * 128, r = idx >> 2, c = (idx & 3) * 8;
+        for (int e = 0; e < 4; ++e) {
+            const int idx = tid + e * 128, r = idx >> 3, c = (idx & 7) * 8;
             const __nv_bfloat16* row = src_row(r);
             const bool there = row && k0 + c < K;
             const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&tile[r][c]);
@@ -110,12 +110,14 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArgs p) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int GB_STAGES = SWIGLU ? 3 : 4;   // 15 KB resp. 10 KB a stage
+    constexpr int GB_STAGES = SWIGLU ? 3 : 4;   // 27 KB resp. 18 KB a stage, in dynamic shared memory
     int g, row0, row_end;
     if (!find_tile(p, g, row0, row_end)) return;
-    __shared__ __align__(16) __nv_bfloat16 As[GB_STAGES][GG_BM][GB_LD];
-    __shared__ __align__(16) __nv_bfloat16 Ws[GB_STAGES][GG_BN][GB_LD];
-    __shared__ __align__(16) __nv_bfloat16 Us[SWIGLU ? GB_STAGES : 1][SWIGLU ? GG_BN : 1][GB_LD];
+    extern __shared__ __align__(16) unsigned char gg_smem[];
+    typedef __nv_bfloat16(*Ring)[GG_BM][GB_LD];   // GG_BM == GG_BN
+    const Ring As = reinterpret_cast<Ring>(gg_smem);
+    const Ring Ws = As + GB_STAGES;
+    const Ring Us = Ws + GB_STAGES;
     __shared__ int64_t a_off[GG_BM];   // where each row of the tile starts in A (-1: beyond the group's rows)
     const int n0 = blockIdx.x * GG_BN;
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.A + p.a_group_cols * g;
@@ -183,7 +185,7 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
                     const uint32_t u0[2] = {b[0], b[1]}, u1[2] = {b[2], b[3]};
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
-                        mma_bf16(acu[i][2 * jj], a[i], u0);
+                            mma_bf16(acu[i][2 * jj], a[i], u0);
                         mma_bf16(acu[i][2 * jj + 1], a[i], u1);
                     }
                 }
@@ -320,7 +322,18 @@ IMP_API int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const v
     if (dtype == IMP_F32)
         e = swiglu ? imp_launch(grouped_gemm_f32_kernel<true>, grid, dim3(256), 0, s, p) : imp_launch(grouped_gemm_f32_kernel<false>, grid, dim3(256), 0, s, p);
     else
-        e = swiglu ? imp_launch(grouped_gemm_bf16_kernel<true>, grid, dim3(128), 0, s, p) : imp_launch(grouped_gemm_bf16_kernel<false>, grid, dim3(128), 0, s, p);
+    {
+        static_assert(GG_BM == GG_BN, "one ring type serves the three tiles");
+        constexpr size_t tile_bytes = (size_t)GG_BM * GB_LD * 2;
+        const size_t smem = swiglu ? 3 * 3 * tile_bytes : 4 * 2 * tile_bytes;
+        static bool raised = false;
+        if (!raised) {
+            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(9 * tile_bytes));
+            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(8 * tile_bytes));
+            raised = true;
+        }
+        e = swiglu ? imp_launch(grouped_gemm_bf16_kernel<true>, grid, dim3(128), smem, s, p) : imp_launch(grouped_gemm_bf16_kernel<false>, grid, dim3(128), smem, s, p);
+    }
     if (e != cudaSuccess) {
         imp_set_error("imp_grouped_gemm: %s", cudaGetErrorString(e));
         return (int)e;
