@@ -43,20 +43,20 @@ __device__ __forceinline__ int64_t gated_row(const GroupedArgs& p, int n, bool u
 }
 
 // Which group and which rows of the list this CTA has; false if it has none.
-__device__ __forceinline__ bool find_tile(const GroupedArgs& p, int& g, int& row0, int& row_end) {
+__device__ __forceinline__ bool find_tile(const GroupedArgs& p, int& g, int& row0, int& row_end, int bm = GG_BM) {
     if (!p.seg) {
         g = blockIdx.z;
-        row0 = blockIdx.y * GG_BM;
+        row0 = blockIdx.y * bm;
         row_end = p.M;
         return row0 < row_end;
     }
     int t = blockIdx.y;
     for (int e = 0; e < p.G; ++e) {
         const int a = p.seg[e], b = p.seg[e + 1];
-        const int nt = (b - a + GG_BM - 1) / GG_BM;
+        const int nt = (b - a + bm - 1) / bm;
         if (t < nt) {
             g = e;
-            row0 = a + t * GG_BM;
+            row0 = a + t * bm;
             row_end = b;
             return true;
         }
@@ -78,13 +78,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 
 // rows x 32 bfloat16 of `src` (row r at src_row(r), null rows zero) into a padded tile.  With `vec` the chunks of 8 travel as
 // asynchronous 16-byte copies (the caller commits and waits); otherwise element by element.
-template <typename RowFn>
+template <int ROWS, typename RowFn>
 __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], RowFn src_row, int k0, int K, int vec, const void* any_global) {
     const int tid = threadIdx.x;
     if (vec) {
-        // 64 rows x 8 chunks of 8: four chunks a thread
+        // ROWS x 8 chunks of 8: four chunks a thread for 64 rows, one for 16
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < ROWS / 16; ++e) {
             const int idx = tid + e * 128, r = idx >> 3, c = (idx & 7) * 8;
             const __nv_bfloat16* row = src_row(r);
             const bool there = row && k0 + c < K;
@@ -93,7 +93,7 @@ __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16 (*tile)[GB_LD], Row
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(there ? 16 : 0) : "memory");
         }
     } else {
-        for (int idx = tid; idx < GG_BM * GB_BK; idx += 128) {
+        for (int idx = tid; idx < ROWS * GB_BK; idx += 128) {
             const int r = idx / GB_BK, c = idx % GB_BK;
             const __nv_bfloat16* row = src_row(r);
             tile[r][c] = (row && k0 + c < K) ? row[k0 + c] : __float2bfloat16_rn(0.f);
@@ -106,24 +106,35 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_r
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
-template <bool SWIGLU>
+// BM rows a tile: 64 (four warps as 2 x 2, 32 x 32 outputs each) or 16 (four warps side by side, 16 x 16 each: steps of few
+// rows a group, where the 64-row tile would spend the tensor pipe and the shared memory on rows that hold nothing).
+template <bool SWIGLU, int BM> struct GroupedTile {
+    static constexpr int STAGES = SWIGLU ? 3 : 4;
+    static constexpr size_t STAGE_ELEMS = (size_t)(BM + GG_BN * (SWIGLU ? 2 : 1)) * GB_LD;
+    static constexpr size_t SMEM = STAGES * STAGE_ELEMS * 2;
+};
+
+template <bool SWIGLU, int BM>
 __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArgs p) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int GB_STAGES = SWIGLU ? 3 : 4;   // 27 KB resp. 18 KB a stage, in dynamic shared memory
+    using Tile = GroupedTile<SWIGLU, BM>;
+    constexpr int GB_STAGES = Tile::STAGES;
+    constexpr int WM = BM == 64 ? 32 : 16, WN = BM == 64 ? 32 : 16, MI = WM / 16, NJ = WN / 16;
     int g, row0, row_end;
-    if (!find_tile(p, g, row0, row_end)) return;
+    if (!find_tile(p, g, row0, row_end, BM)) return;
     extern __shared__ __align__(16) unsigned char gg_smem[];
-    typedef __nv_bfloat16(*Ring)[GG_BM][GB_LD];   // GG_BM == GG_BN
-    const Ring As = reinterpret_cast<Ring>(gg_smem);
-    const Ring Ws = As + GB_STAGES;
-    const Ring Us = Ws + GB_STAGES;
-    __shared__ int64_t a_off[GG_BM];   // where each row of the tile starts in A (-1: beyond the group's rows)
+    typedef __nv_bfloat16(*TilePtr)[GB_LD];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(gg_smem);
+    auto As = [&](int st) { return reinterpret_cast<TilePtr>(ring + st * Tile::STAGE_ELEMS); };
+    auto Ws = [&](int st) { return reinterpret_cast<TilePtr>(ring + st * Tile::STAGE_ELEMS + (size_t)BM * GB_LD); };
+    auto Us = [&](int st) { return reinterpret_cast<TilePtr>(ring + st * Tile::STAGE_ELEMS + (size_t)(BM + GG_BN) * GB_LD); };
+    __shared__ int64_t a_off[BM];   // where each row of the tile starts in A (-1: beyond the group's rows)
     const int n0 = blockIdx.x * GG_BN;
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.A + p.a_group_cols * g;
     const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + p.w_group_stride * g;
     const __nv_bfloat16* U = SWIGLU ? (p.il ? W : (const __nv_bfloat16*)p.W2 + p.w_group_stride * g) : nullptr;
-    if (threadIdx.x < GG_BM) {
+    if (threadIdx.x < BM) {
         const int lr = row0 + threadIdx.x;
         a_off[threadIdx.x] = lr < row_end ? (int64_t)(p.a_rows ? p.a_rows[lr] : lr) * p.lda : -1;
     }
@@ -133,16 +144,16 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
     auto u_row = [&](int r) -> const __nv_bfloat16* { return n0 + r < p.N ? U + gated_row(p, n0 + r, true) * p.ldw : nullptr; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
-    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int wm = BM == 64 ? (warp >> 1) * 32 : 0, wn = BM == 64 ? (warp & 1) * 32 : warp * 16;
     // what a lane hands to ldmatrix: for A (16 rows x 16 k) row lane % 16 at k + 8 * (lane / 16); for W (16 n x 16 k, two
     // 8-column tiles of the product) row lane % 8 + 8 * (lane / 16) at k + 8 * ((lane / 8) % 2)
     const int a_r = lane & 15, a_c = (lane >> 4) * 8;
     const int b_r = (lane & 7) + (lane >> 4) * 8, b_c = ((lane >> 3) & 1) * 8;
-    float acc[2][4][4], acu[SWIGLU ? 2 : 1][4][4];
+    float acc[MI][2 * NJ][4], acu[SWIGLU ? MI : 1][2 * NJ][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 2 * NJ; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 acc[i][j][e] = 0.f;
@@ -153,9 +164,9 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
     auto fetch = [&](int kb) {
         if (kb < n_k) {
             const int st = kb % GB_STAGES;
-            load_tile_bf16(As[st], a_row, kb * GB_BK, p.K, p.vec, p.W);
-            load_tile_bf16(Ws[st], w_row, kb * GB_BK, p.K, p.vec, p.W);
-            if (SWIGLU) load_tile_bf16(Us[st], u_row, kb * GB_BK, p.K, p.vec, p.W);
+            load_tile_bf16<BM>(As(st), a_row, kb * GB_BK, p.K, p.vec, p.W);
+            load_tile_bf16<GG_BN>(Ws(st), w_row, kb * GB_BK, p.K, p.vec, p.W);
+            if (SWIGLU) load_tile_bf16<GG_BN>(Us(st), u_row, kb * GB_BK, p.K, p.vec, p.W);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");   // one group per k-block, empty ones included: the wait counts groups
     };
@@ -165,27 +176,28 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
         __syncthreads();                 // block kb has landed for everyone, and block kb - 1's stage is free again
         fetch(kb + GB_STAGES - 1);
         const int st = kb % GB_STAGES;
+        const TilePtr as = As(st), ws = Ws(st), us = Us(st);
 #pragma unroll
         for (int kk = 0; kk < GB_BK; kk += 16) {
-            uint32_t a[2][4];
+            uint32_t a[MI][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) ldmatrix_x4(a[i], &As[st][wm + i * 16 + a_r][kk + a_c]);
+            for (int i = 0; i < MI; ++i) ldmatrix_x4(a[i], &as[wm + i * 16 + a_r][kk + a_c]);
 #pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
+            for (int jj = 0; jj < NJ; ++jj) {
                 uint32_t b[4];
-                ldmatrix_x4(b, &Ws[st][wn + jj * 16 + b_r][kk + b_c]);
+                ldmatrix_x4(b, &ws[wn + jj * 16 + b_r][kk + b_c]);
                 const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
+                for (int i = 0; i < MI; ++i) {
                     mma_bf16(acc[i][2 * jj], a[i], b0);
                     mma_bf16(acc[i][2 * jj + 1], a[i], b1);
                 }
                 if (SWIGLU) {
-                    ldmatrix_x4(b, &Us[st][wn + jj * 16 + b_r][kk + b_c]);
+                    ldmatrix_x4(b, &us[wn + jj * 16 + b_r][kk + b_c]);
                     const uint32_t u0[2] = {b[0], b[1]}, u1[2] = {b[2], b[3]};
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                            mma_bf16(acu[i][2 * jj], a[i], u0);
+                    for (int i = 0; i < MI; ++i) {
+                        mma_bf16(acu[i][2 * jj], a[i], u0);
                         mma_bf16(acu[i][2 * jj + 1], a[i], u1);
                     }
                 }
@@ -194,14 +206,14 @@ __global__ void __launch_bounds__(128) grouped_gemm_bf16_kernel(const GroupedArg
     }
     __nv_bfloat16* C = (__nv_bfloat16*)p.C + p.c_group_cols * g;
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int lr = row0 + wm + i * 16 + gid + half * 8;
             if (lr >= row_end) continue;
             __nv_bfloat16* crow = C + (int64_t)lr * p.ldc;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 2 * NJ; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int n = n0 + wn + j * 8 + 2 * tig + e;
@@ -314,25 +326,30 @@ IMP_API int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const v
              aligned(A) && aligned(W) && aligned(W2))
                 ? 1
                 : 0;
-    const int row_tiles = seg ? (M + GG_BM - 1) / GG_BM + G : (M + GG_BM - 1) / GG_BM;
-    IMP_CHECK_ARG(row_tiles <= 65535 && G <= 65535, "imp_grouped_gemm: too many row tiles or groups for one launch");
-    const dim3 grid((N + GG_BN - 1) / GG_BN, row_tiles, seg ? 1 : G);
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    if (dtype == IMP_F32)
+    // few rows a group (a decode step's experts, its per-head products): 16-row tiles
+    const int bm = (dtype != IMP_F32 && (seg ? M / G : M) < 16) ? 16 : GG_BM;
+    const int row_tiles = seg ? (M + bm - 1) / bm + G : (M + bm - 1) / bm;
+    IMP_CHECK_ARG(row_tiles <= 65535 && G <= 65535, "imp_grouped_gemm: too many row tiles or groups for one launch");
+    const dim3 grid((N + GG_BN - 1) / GG_BN, row_tiles, seg ? 1 : G);
+    if (dtype == IMP_F32) {
         e = swiglu ? imp_launch(grouped_gemm_f32_kernel<true>, grid, dim3(256), 0, s, p) : imp_launch(grouped_gemm_f32_kernel<false>, grid, dim3(256), 0, s, p);
-    else
-    {
-        static_assert(GG_BM == GG_BN, "one ring type serves the three tiles");
-        constexpr size_t tile_bytes = (size_t)GG_BM * GB_LD * 2;
-        const size_t smem = swiglu ? 3 * 3 * tile_bytes : 4 * 2 * tile_bytes;
+    } else {
         static bool raised = false;
         if (!raised) {
-            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(9 * tile_bytes));
-            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(8 * tile_bytes));
+            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GroupedTile<true, 64>::SMEM);
+            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GroupedTile<false, 64>::SMEM);
+            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GroupedTile<true, 16>::SMEM);
+            cudaFuncSetAttribute(grouped_gemm_bf16_kernel<false, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GroupedTile<false, 16>::SMEM);
             raised = true;
         }
-        e = swiglu ? imp_launch(grouped_gemm_bf16_kernel<true>, grid, dim3(128), smem, s, p) : imp_launch(grouped_gemm_bf16_kernel<false>, grid, dim3(128), smem, s, p);
+        if (bm == 16)
+            e = swiglu ? imp_launch(grouped_gemm_bf16_kernel<true, 16>, grid, dim3(128), GroupedTile<true, 16>::SMEM, s, p)
+                       : imp_launch(grouped_gemm_bf16_kernel<false, 16>, grid, dim3(128), GroupedTile<false, 16>::SMEM, s, p);
+        else
+            e = swiglu ? imp_launch(grouped_gemm_bf16_kernel<true, 64>, grid, dim3(128), GroupedTile<true, 64>::SMEM, s, p)
+                       : imp_launch(grouped_gemm_bf16_kernel<false, 64>, grid, dim3(128), GroupedTile<false, 64>::SMEM, s, p);
     }
     if (e != cudaSuccess) {
         imp_set_error("imp_grouped_gemm: %s", cudaGetErrorString(e));
