@@ -376,8 +376,14 @@ MODELS = {
                        {"type": "latent_attention", "mixer": latent(5, 32, 8, 16, 56, 40, base=200.0), "mlp": moe_cfg(9, 2, 32, 48)},
                        {"type": "latent_attention", "mixer": latent(3, 20, 6, 12, 36, 16, base=10000.0), "mlp": None}],
             "loop": {"start": 1, "stop": 3, "times": 2}}, 16, 12),
+    # Z3: one layer runs three times between a layer that runs once before it and one after it; a cached vector of 96
+    "Z3": ({"architecture": "Kuzipel", "vocab": 130, "width": 96, "norm": {"eps": 1e-5}, "residual_mult": 1.0,
+            "layers": [{"type": "latent_attention", "mixer": latent(6, 16, 16, 16, 80, 48, base=50.0), "mlp": None},
+                       {"type": "wkv", "mixer": {"heads": 3, "dim": 32}, "mlp": moe_cfg(8, 2, 40, 32)},
+                       {"type": "latent_attention", "mixer": latent(2, 48, 32, 40, 64, 32), "mlp": moe_cfg(5, 4, 24, 0)}],
+            "loop": {"start": 1, "stop": 2, "times": 3}}, 8, 16),
 }
-LENGTHS = {"Z1": (1, 23, 75, 40, 130, 64), "Z2": (150, 2, 33, 201, 64, 97)}
+LENGTHS = {"Z1": (1, 23, 75, 40, 130, 64), "Z2": (150, 2, 33, 201, 64, 97), "Z3": (70, 5, 140, 31, 64, 2)}
 
 
 def make_weights(cfg, rank, seed):
@@ -425,9 +431,14 @@ def kuzipel_folders(tmp_path_factory):
     return out
 
 
-def check_rows(rows, reqs, ref, dtype, label="", unsure=()):
+# bfloat16: the bound on the 95th percentile of the rows' errors.  Z3's layers add about 0.4 % a run in the median (its
+# float32 errors times 2^14, growing evenly from run to run), 7 % at the 95th percentile over all its requests.
+P95 = {"Z1": 0.04, "Z2": 0.04, "Z3": 0.10}
+
+
+def check_rows(rows, reqs, ref, dtype, label="", unsure=(), p95=0.04):
     """float32: every logit to 1e-4 of the largest.  bfloat16: a row's root-mean-square error against the root mean square
-    of all logits is at most 4 % for 95 of 100 rows and 30 % for every row; rows in `unsure` (a router's choice for that
+    of all logits is at most `p95` for 95 of 100 rows and 30 % for every row; rows in `unsure` (a router's choice for that
     token hangs on less than the rounding of its 16-bit input moves a logit) are not judged."""
     scale = max(float(np.abs(r).max()) for r in ref.values())
     rms_all = float(np.sqrt(np.mean(np.concatenate([r.ravel() for r in ref.values()]) ** 2)))
@@ -445,11 +456,11 @@ def check_rows(rows, reqs, ref, dtype, label="", unsure=()):
             n += 1
     assert n == sum(len(v) for v in reqs.values())
     if rel:
-        assert float(np.quantile(rel, 0.95)) <= 0.04, f"{label}: 95th percentile of the rows' rms error {np.quantile(rel, 0.95):.3g} in {dtype}"
+        assert float(np.quantile(rel, 0.95)) <= p95, f"{label}: 95th percentile of the rows' rms error {np.quantile(rel, 0.95):.3g} in {dtype}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["Z1", "Z2"])
+@pytest.mark.parametrize("name", ["Z1", "Z2", "Z3"])
 def test_replay_all_ways_of_cutting(name, dtype, kuzipel_folders, tmp_path):
     folder, cfg, page, W, reqs, ref, unsure = kuzipel_folders[name]
     assert len(unsure) < sum(len(v) for v in reqs.values()) // 3
@@ -461,14 +472,14 @@ def test_replay_all_ways_of_cutting(name, dtype, kuzipel_folders, tmp_path):
     for label, steps, pool in cuts:
         out = run_trace(folder, dtype, steps, pool, str(tmp_path / label), V, page_size=page)
         rows = collect(steps, out)
-        check_rows(rows, reqs, ref, dtype, label, unsure)
+        check_rows(rows, reqs, ref, dtype, label, unsure, P95[name])
         results[label] = rows
     steps, peak = mixed(reqs)
     assert max(len(s["entries"]) for s in steps) == 4
     assert peak < sum(round64(len(v)) for v in reqs.values()), "the pool must be too small to avoid reuse"
     out = run_trace(folder, dtype, steps, peak, str(tmp_path / "mixed"), V, page_size=page)
     rows = collect(steps, out)
-    check_rows(rows, reqs, ref, dtype, "mixed", unsure)
+    check_rows(rows, reqs, ref, dtype, "mixed", unsure, P95[name])
     results["mixed"] = rows
     if dtype == "float32":
         # every reduction of the float32 path has an order that depends on the row alone
