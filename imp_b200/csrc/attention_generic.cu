@@ -74,9 +74,18 @@ __global__ void paged_attention_generic_kernel(
             } else {
                 off = (((int64_t)page * Hkv + hk) * page_size + (j % page_size)) * Dh;
                 const TA* kp = k_cache + off;
-                float dot = 0.f;
-                for (int d = 0; d < Dh; ++d) dot = fmaf(q_s[d], to_float(kp[d]), dot);
-                s = dot * scale;
+                // four interleaved partial sums (entries d, d + 1, d + 2, d + 3 of every group of four), added at the end:
+                // shorter chains than one sum over the whole head, in an order the head size alone fixes
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                int d = 0;
+                for (; d + 3 < Dh; d += 4) {
+                    d0 = fmaf(q_s[d], to_float(kp[d]), d0);
+                    d1 = fmaf(q_s[d + 1], to_float(kp[d + 1]), d1);
+                    d2 = fmaf(q_s[d + 2], to_float(kp[d + 2]), d2);
+                    d3 = fmaf(q_s[d + 3], to_float(kp[d + 3]), d3);
+                }
+                for (; d < Dh; ++d) d0 = fmaf(q_s[d], to_float(kp[d]), d0);
+                s = ((d0 + d1) + (d2 + d3)) * scale;
                 if (bias_h) s += bias_h[min(pos - j, n_dist - 1)];
             }
         }
@@ -93,10 +102,11 @@ __global__ void paged_attention_generic_kernel(
         for (int a = 0; a < ATT_ACC; ++a) {
             const int dim = tid + a * ATT_BLOCK;
             if (dim < Dh) {
-                float sum = acc[a] * corr;
+                // the chunk's 128 keys are summed on their own and then added to the running sum
+                float part = 0.f;
                 for (int i = 0; i < n_here; ++i)
-                    if (off_s[i] >= 0) sum = fmaf(p_s[i], to_float(v_cache[off_s[i] + dim]), sum);
-                acc[a] = sum;
+                    if (off_s[i] >= 0) part = fmaf(p_s[i], to_float(v_cache[off_s[i] + dim]), part);
+                acc[a] = fmaf(acc[a], corr, part);
             }
         }
         __syncthreads();  // p_s/off_s are rewritten by the next chunk

@@ -11,8 +11,8 @@
 //
 // bfloat16: mma.sync m16n8k16 with 32-bit accumulation, 64 x 64 x 64 tiles through a cp.async ring of three or four stages,
 // fragments by ldmatrix, four warps.  (Tiles of 128 x 64 and 128 x 128 measured no faster for many rows a group and slower
-// for few; skipping the products of 16-row pieces without rows measured slower too.)  float32: FFMA with k
-// ascending for every output element, so a row's result does not depend on what else is in the batch.
+// for few; skipping the products of 16-row pieces without rows measured slower too.)  float32: FFMA, k ascending in blocks
+// of 16 whose sums are added in order, for every output element, so a row's result does not depend on what else is in the batch.
 #include <algorithm>
 
 #include "common.cuh"
@@ -269,6 +269,15 @@ __global__ void __launch_bounds__(256) grouped_gemm_f32_kernel(const GroupedArgs
             if (SWIGLU) Us[kk][r] = (gn < p.N && gk < p.K) ? U[gated_row(p, gn, true) * p.ldw + gk] : 0.f;
         }
         __syncthreads();
+        // a block's 16 products are summed on their own and then added to the running sum (as in gemm_f32.cu)
+        float blk[4][4], blu[SWIGLU ? 4 : 1][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                blk[i][j] = 0.f;
+                if (SWIGLU) blu[i][j] = 0.f;
+            }
 #pragma unroll
         for (int kk = 0; kk < GF_BK; ++kk) {
             float a[4], w[4], u[4];
@@ -283,10 +292,17 @@ __global__ void __launch_bounds__(256) grouped_gemm_f32_kernel(const GroupedArgs
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
-                    if (SWIGLU) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+                    blk[i][j] = fmaf(a[i], w[j], blk[i][j]);
+                    if (SWIGLU) blu[i][j] = fmaf(a[i], u[j], blu[i][j]);
                 }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[i][j] += blk[i][j];
+                if (SWIGLU) acu[i][j] += blu[i][j];
+            }
         __syncthreads();
     }
     float* C = (float*)p.C + p.c_group_cols * g;

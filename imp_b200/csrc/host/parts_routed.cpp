@@ -199,7 +199,8 @@ struct LatentAttention : Mixer {
 // decay reads the input mixed with the previous token's, x + (x_prev - x) * mu_s; r, k, v = W_s mix_s; gate =
 // silu(W_g mix_g); decay = exp(-exp(W_2 tanh(W_1 mix_w) + w0)) per head and key channel; the read-out adds a bonus u for
 // the current token; each head's result is divided by its root mean square, times a weight, times the gate; then W_o.
-// State per request: S (H heads of D x D) and the last input row, both float32, zero at the start.
+// State per request: S (H heads of D x D; 32-bit in the bfloat16 path, 64-bit in the float32 path, whose read-out would
+// otherwise lose five digits where a head's sum nearly cancels) and the last input row (float32), zero at the start.
 //
 // params: hidden_size, num_heads, head_dim, norm_eps, decay_rank (0 or absent: the rows of the checkpoint's W_1).
 struct Wkv : Mixer {
@@ -229,7 +230,8 @@ struct Wkv : Mixer {
         const int64_t d = need_int(p, "hidden_size", me), H = need_int(p, "num_heads", me), D = need_int(p, "head_dim", me);
         CacheSpec s;
         s.kind = CacheSpec::State;
-        s.states.push_back(StateTensorSpec{"S", {H, D, D}, F32});
+        // room for S as 64-bit words: the float32 path carries the state in 64-bit (see csrc/wkv.cu), bfloat16 uses half of it
+        s.states.push_back(StateTensorSpec{"S", {H, D, 2 * D}, F32});
         s.states.push_back(StateTensorSpec{"prev", {d}, F32});
         return s;
     }

@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(WKV_COLS* WKV_LANES) wkv_scan_kernel(const TA*
     if (t1 <= t0) return;
     const int tid = threadIdx.x, j = j0 + tid / WKV_LANES, sub = tid % WKV_LANES, lane = tid & 31, warp = tid >> 5;
     const bool col = j < D;
-    float* S = state + ((int64_t)slots[seq] * H + h) * D * D;
+    float* S = state + (int64_t)slots[seq] * H * D * D * 2 + (int64_t)h * D * D;   // a slot has room for 64-bit words; this path uses half
     float s[RPT];
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) {
@@ -205,6 +205,88 @@ __global__ void __launch_bounds__(WKV_COLS* WKV_LANES) wkv_scan_kernel(const TA*
     }
 }
 
+// The float32 path carries the state, the decay and the read-out in 64-bit.  A state of slowly decaying channels is a sum
+// over hundreds of tokens; where a head's read-out nearly cancels (its root mean square a few per cent of the usual), the
+// rounding of a 32-bit state, 1e-6 of the state after so many steps, becomes 1e-5 and more of the normalised result.  The
+// slot holds the doubles' words, so a prompt cut anywhere continues from the same bits.  Same layout of the work as above,
+// without its tuning: this path is the sharper one, not the fast one.
+template <int RPT>
+__global__ void __launch_bounds__(WKV_COLS* WKV_LANES) wkv_scan_f64_kernel(const float* __restrict__ r, const float* __restrict__ k,
+                                                                            const float* __restrict__ v, int64_t ld, const float* __restrict__ dlog,
+                                                                            const float* __restrict__ w0, const float* __restrict__ u,
+                                                                            float* __restrict__ state, float* __restrict__ out,
+                                                                            const int* __restrict__ q_start, const int* __restrict__ slots, int H, int D,
+                                                                            int col_blocks) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int DP = RPT * WKV_LANES, CH = 8;
+    __shared__ double s_w[CH][DP], s_b[CH];
+    __shared__ float s_r[CH][DP], s_k[CH][DP], s_v[CH][WKV_COLS];
+    const int h = blockIdx.x / col_blocks, j0 = (blockIdx.x % col_blocks) * WKV_COLS, seq = blockIdx.y;
+    const int t0 = q_start[seq], t1 = q_start[seq + 1];
+    if (t1 <= t0) return;
+    const int tid = threadIdx.x, j = j0 + tid / WKV_LANES, sub = tid % WKV_LANES, lane = tid & 31, warp = tid >> 5;
+    const bool col = j < D;
+    double* S = reinterpret_cast<double*>(state) + ((int64_t)slots[seq] * H + h) * D * D;
+    double s[RPT];
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+        const int i = sub * RPT + ii;
+        s[ii] = (col && i < D) ? S[(int64_t)i * D + j] : 0.0;
+    }
+    const int64_t hoff = (int64_t)h * D;
+    for (int c0 = t0; c0 < t1; c0 += CH) {
+        const int n = min(CH, t1 - c0);
+        __syncthreads();   // the chunk before has been read
+        for (int e = tid; e < n * DP; e += blockDim.x) {
+            const int tt = e / DP, i = e % DP;
+            float rv = 0.f, kv = 0.f;
+            double wv = 1.0;
+            if (i < D) {
+                const int64_t at = (int64_t)(c0 + tt) * ld + hoff + i;
+                rv = r[at];
+                kv = k[at];
+                wv = exp(-exp((double)dlog[(int64_t)(c0 + tt) * H * D + hoff + i] + (double)w0[hoff + i]));
+            }
+            s_r[tt][i] = rv, s_k[tt][i] = kv, s_w[tt][i] = wv;
+        }
+        for (int e = tid; e < n * WKV_COLS; e += blockDim.x) {
+            const int tt = e / WKV_COLS, c = e % WKV_COLS;
+            s_v[tt][c] = j0 + c < D ? v[(int64_t)(c0 + tt) * ld + hoff + j0 + c] : 0.f;
+        }
+        __syncthreads();
+        for (int tt = warp; tt < n; tt += (int)(blockDim.x >> 5)) {
+            double b = 0.0;
+            for (int i = lane; i < D; i += 32) b = fma((double)s_r[tt][i] * (double)u[hoff + i], (double)s_k[tt][i], b);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) b += __shfl_xor_sync(0xffffffffu, b, o);
+            if (lane == 0) s_b[tt] = b;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const double vj = (double)s_v[tt][tid / WKV_LANES];
+            double a0 = 0.0, a1 = 0.0;
+#pragma unroll
+            for (int ii = 0; ii < RPT; ii += 2) {
+                a0 = fma((double)s_r[tt][sub * RPT + ii], s[ii], a0);
+                a1 = fma((double)s_r[tt][sub * RPT + ii + 1], s[ii + 1], a1);
+            }
+            double o = a0 + a1;
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o = fma(vj, s_b[tt], o);
+#pragma unroll
+            for (int ii = 0; ii < RPT; ++ii) s[ii] = fma(s_w[tt][sub * RPT + ii], s[ii], (double)s_k[tt][sub * RPT + ii] * vj);
+            if (col && sub == 0) out[(int64_t)(c0 + tt) * H * D + hoff + j] = (float)o;
+        }
+    }
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+        const int i = sub * RPT + ii;
+        if (col && i < D) S[(int64_t)i * D + j] = s[ii];
+    }
+}
+
 // y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(g): one warp per (token, head).
 template <typename TA>
 __global__ void wkv_output_kernel(TA* __restrict__ y, const float* __restrict__ o, const TA* __restrict__ g, int64_t ldg,
@@ -231,6 +313,11 @@ cudaError_t launch_scan(const void* r, const void* k, const void* v, int64_t ld,
                         float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, cudaStream_t s) {
     // an ordinary dependent: its CTAs hold many registers and would sit on the SMs while the kernels before it run
     const int col_blocks = (D + WKV_COLS - 1) / WKV_COLS;
+    if (sizeof(TA) == 4) {
+        wkv_scan_f64_kernel<RPT><<<dim3(H * col_blocks, n_seqs), WKV_COLS * WKV_LANES, 0, s>>>((const float*)r, (const float*)k, (const float*)v, ld, dlog, w0, u,
+                                                                                             state, out, q_start, slots, H, D, col_blocks);
+        return cudaGetLastError();
+    }
     wkv_scan_kernel<TA, RPT><<<dim3(H * col_blocks, n_seqs), WKV_COLS * WKV_LANES, 0, s>>>((const TA*)r, (const TA*)k, (const TA*)v, ld, dlog, w0, u, state, out,
                                                                                          q_start, slots, H, D, col_blocks);
     return cudaGetLastError();
@@ -288,7 +375,8 @@ IMP_API int imp_tanh_inplace(void* x, int64_t n, int dtype, void* stream) {
 }
 
 // r, k, v: [T, H*D] of the activation type, rows ld apart (three tensors with one stride); dlog: float32 [T, H*D]
-// dense; w0: [H*D]; u: [H, D]; state: [slots, H, D, D]; out: float32 [T, H*D] dense.
+// dense; w0: [H*D]; u: [H, D]; state: [slots, H, D, 2 D] float32 words (float32 activations: [slots, H, D, D] doubles; bfloat16:
+// the first H*D*D floats of a slot); out: float32 [T, H*D] dense.
 IMP_API int imp_wkv_scan(const void* r, const void* k, const void* v, int64_t ld, const float* dlog, const float* w0, const float* u,
                          float* state, float* out, const int* q_start, const int* slots, int n_seqs, int H, int D, int act_dtype,
                          void* stream) {

@@ -93,7 +93,7 @@ def test_caches_one_per_run_and_keys_only_for_the_latent():
     spec = mixer_cache_spec("latent_attention", plan_for(config_from_dict(CFG)).layers[1].mixer.params)
     assert spec == {"kind": "paged", "num_kv_heads": 1, "head_dim": 48, "window": 0, "keys_only": True}
     state = mixer_cache_spec("wkv", plan_for(config_from_dict(CFG)).layers[0].mixer.params)
-    assert [(t["name"], t["shape"], t["dtype"]) for t in state["tensors"]] == [("S", [2, 24, 24], "float32"), ("prev", [64], "float32")]
+    assert [(t["name"], t["shape"], t["dtype"]) for t in state["tensors"]] == [("S", [2, 24, 48], "float32"), ("prev", [64], "float32")]   # S with room for 64-bit words
     # run positions: wkv, map, latent(48), latent(64), map, latent(48), latent(64): the repeated layers own a cache per pass
     spec2 = mixer_cache_spec("latent_attention", plan_for(config_from_dict(CFG)).layers[2].mixer.params)
     mgr = CacheManager([state, None, spec, spec2, None, spec, spec2], page_size=4, num_pages=32, num_state_slots=2)
